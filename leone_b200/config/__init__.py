@@ -1,6 +1,7 @@
 from .base import (ConfigError, InvalidValue, MissingKey, ModelConfig, UnsupportedArchitecture,
                    UnsupportedField, WrongType, read_config_json)
 from .qwen3 import Qwen3Config
+from .sarizen import SarizenConfig
 
 __all__ = ["ConfigError", "InvalidValue", "MissingKey", "ModelConfig", "UnsupportedArchitecture",
-           "UnsupportedField", "WrongType", "read_config_json", "Qwen3Config"]
+           "UnsupportedField", "WrongType", "read_config_json", "Qwen3Config", "SarizenConfig"]

@@ -46,10 +46,11 @@ _ABSENT = object()
 class ConfigReader:
     """Checked access to the keys of one ``config.json`` mapping."""
 
-    def __init__(self, raw: Mapping[str, Any]):
+    def __init__(self, raw: Mapping[str, Any], where: str = "config.json"):
         if not isinstance(raw, Mapping):
-            raise WrongType("config.json must hold a JSON object")
+            raise WrongType(f"{where} must hold a JSON object")
         self.raw = raw
+        self.where = where
 
     def has(self, key: str) -> bool:
         return key in self.raw and self.raw[key] is not None
@@ -57,13 +58,13 @@ class ConfigReader:
     def positive_int(self, key: str, default: Any = _ABSENT) -> int:
         if not self.has(key):
             if default is _ABSENT:
-                raise MissingKey(f"config.json: missing key '{key}'")
+                raise MissingKey(f"{self.where}: missing key '{key}'")
             return default
         value = self.raw[key]
         if isinstance(value, bool) or not isinstance(value, int):
-            raise WrongType(f"config.json: '{key}' must be an integer, got {value!r}")
+            raise WrongType(f"{self.where}: '{key}' must be an integer, got {value!r}")
         if value <= 0:
-            raise InvalidValue(f"config.json: '{key}' must be > 0, got {value}")
+            raise InvalidValue(f"{self.where}: '{key}' must be > 0, got {value}")
         return value
 
     def optional_int(self, key: str) -> int | None:
@@ -71,20 +72,20 @@ class ConfigReader:
             return None
         value = self.raw[key]
         if isinstance(value, bool) or not isinstance(value, int):
-            raise WrongType(f"config.json: '{key}' must be an integer, got {value!r}")
+            raise WrongType(f"{self.where}: '{key}' must be an integer, got {value!r}")
         return value
 
     def positive_float(self, key: str, default: Any = _ABSENT) -> float:
         if not self.has(key):
             if default is _ABSENT:
-                raise MissingKey(f"config.json: missing key '{key}'")
+                raise MissingKey(f"{self.where}: missing key '{key}'")
             return default
         value = self.raw[key]
         if isinstance(value, bool) or not isinstance(value, (int, float)):
-            raise WrongType(f"config.json: '{key}' must be a number, got {value!r}")
+            raise WrongType(f"{self.where}: '{key}' must be a number, got {value!r}")
         value = float(value)
         if not math.isfinite(value) or value <= 0.0:
-            raise InvalidValue(f"config.json: '{key}' must be finite and > 0, got {value}")
+            raise InvalidValue(f"{self.where}: '{key}' must be finite and > 0, got {value}")
         return value
 
     def boolean(self, key: str, default: bool) -> bool:
@@ -92,23 +93,48 @@ class ConfigReader:
             return default
         value = self.raw[key]
         if not isinstance(value, bool):
-            raise WrongType(f"config.json: '{key}' must be true or false, got {value!r}")
+            raise WrongType(f"{self.where}: '{key}' must be true or false, got {value!r}")
         return value
 
     def string(self, key: str, default: Any = _ABSENT) -> str:
         if not self.has(key):
             if default is _ABSENT:
-                raise MissingKey(f"config.json: missing key '{key}'")
+                raise MissingKey(f"{self.where}: missing key '{key}'")
             return default
         value = self.raw[key]
         if not isinstance(value, str):
-            raise WrongType(f"config.json: '{key}' must be a string, got {value!r}")
+            raise WrongType(f"{self.where}: '{key}' must be a string, got {value!r}")
+        return value
+
+    def section(self, key: str, optional: bool = False) -> "ConfigReader | None":
+        """A nested JSON object under ``key`` as a reader of its own (messages name the path)."""
+        if not self.has(key):
+            if optional:
+                return None
+            raise MissingKey(f"{self.where}: missing key '{key}'")
+        value = self.raw[key]
+        if not isinstance(value, Mapping):
+            raise WrongType(f"{self.where}: '{key}' must be an object, got {value!r}")
+        return ConfigReader(value, f"{self.where}: {key}")
+
+    def number(self, key: str, default: Any = _ABSENT) -> float:
+        """A finite number of either sign."""
+        if not self.has(key):
+            if default is _ABSENT:
+                raise MissingKey(f"{self.where}: missing key '{key}'")
+            return default
+        value = self.raw[key]
+        if isinstance(value, bool) or not isinstance(value, (int, float)):
+            raise WrongType(f"{self.where}: '{key}' must be a number, got {value!r}")
+        value = float(value)
+        if not math.isfinite(value):
+            raise InvalidValue(f"{self.where}: '{key}' must be finite, got {value}")
         return value
 
     def must_be_absent_or(self, key: str, allowed: tuple, why: str) -> None:
         if key in self.raw and self.raw[key] not in allowed:
             raise UnsupportedField(
-                f"config.json: '{key}' = {self.raw[key]!r} is not supported ({why})")
+                f"{self.where}: '{key}' = {self.raw[key]!r} is not supported ({why})")
 
 
 @dataclass(frozen=True)
@@ -178,7 +204,13 @@ def read_config_json(folder: str) -> dict:
 
 
 def architecture_name(raw: Mapping[str, Any]) -> str:
+    """The model class a ``config.json`` names: the first entry of ``architectures`` (a list), or
+    the string under ``architecture``."""
+    single = raw.get("architecture")
+    if "architectures" not in raw and isinstance(single, str) and single:
+        return single
     names = raw.get("architectures")
     if not isinstance(names, list) or len(names) < 1 or not isinstance(names[0], str):
-        raise MissingKey("config.json: 'architectures' must be a list with the model class name")
+        raise MissingKey("config.json: 'architectures' must be a list with the model class name "
+                         "(or 'architecture' a string)")
     return names[0]

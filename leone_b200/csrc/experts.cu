@@ -1,0 +1,342 @@
+// Routed experts: router, grouping of (token, choice) pairs by expert, grouped products, combine.
+//
+//   z = W_router x (fp32),  s = sigmoid(z) or softmax(z),  the `top` largest s are chosen
+//   (lowest index first on equal scores); a pair's weight is its s, optionally divided by the sum
+//   of the chosen.  The weight multiplies the expert's input (`scale_input`) or its output.
+//   expert_e(a) = W_down_e (silu(W_gate_e a) * (W_up_e a))
+//   out[t] += sum over the token's pairs, in the order of choice.
+//
+// Nothing is read back by the host: the pairs are counted and placed per expert on the device, and
+// the grouped products take a grid that is large enough for any assignment (row tiles that turn out
+// to be empty return at once).  A row of the grouped products is computed from its own token only,
+// with k ascending, so a token's result does not depend on what else is in the step.
+#include "common.cuh"
+
+namespace leone {
+
+__device__ __forceinline__ float silu_e(float z) { return z / (1.f + expf(-z)); }
+
+// One warp per token.
+template <typename T>
+__global__ void __launch_bounds__(128)
+route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, int n_tokens, int width, int experts,
+             int top, int softmax, int renormalize, int* __restrict__ chosen, float* __restrict__ weight) {
+  extern __shared__ __align__(16) float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  float* sc = smem + (size_t)warp * experts;
+  const T* row = x + (size_t)t * ldx;
+  for (int e = 0; e < experts; ++e) {
+    const T* we = w + (size_t)e * width;
+    float dot = 0.f;
+    for (int c = lane; c < width; c += 32) dot = fmaf(to_float<T>(row[c]), to_float<T>(we[c]), dot);
+    dot = warp_sum(dot);
+    if (lane == 0) sc[e] = dot;
+  }
+  __syncwarp();
+  if (softmax) {
+    float m = -INFINITY;
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, sc[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) sum += expf(sc[e] - m);
+    sum = warp_sum(sum);
+    for (int e = lane; e < experts; e += 32) sc[e] = expf(sc[e] - m) / sum;
+  } else {
+    for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+  }
+  __syncwarp();
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = sc[e];
+      if (v > best) { best = v; at = e; }          // ascending e: the lowest index of equal scores
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (lane == 0) {
+      chosen[(size_t)t * top + j] = at;
+      weight[(size_t)t * top + j] = best;
+      sc[at] = -INFINITY;
+    }
+    total += best;
+    __syncwarp();
+  }
+  if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
+}
+
+// One block: counts per expert, their prefix sums, and every pair's row among its expert's.
+// offsets: [experts + 1]; order: [pairs] (sorted row -> pair).
+__global__ void __launch_bounds__(1024)
+group_pairs_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __restrict__ offsets,
+                   int* __restrict__ order) {
+  extern __shared__ int count_s[];      // [experts] counts, then cursors
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count_s[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = chosen[p];
+    if (e >= 0 && e < experts) atomicAdd(&count_s[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int c = count_s[e];
+      offsets[e] = run;
+      count_s[e] = run;
+      run += c;
+    }
+    offsets[experts] = run;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = chosen[p];
+    if (e >= 0 && e < experts) order[atomicAdd(&count_s[e], 1)] = p;
+  }
+}
+
+constexpr int GM = 32, GN = 64, GK = 16;
+
+// Which expert and which of its rows the row tile `tile` covers; false if past the last tile.
+__device__ __forceinline__ bool find_tile(const int* __restrict__ offsets, int experts, int tile, int& expert,
+                                          int& row0, int& row1) {
+  int before = 0;
+  for (int e = 0; e < experts; ++e) {
+    const int b = offsets[e], n = offsets[e + 1] - b;
+    const int tiles = (n + GM - 1) / GM;
+    if (tile < before + tiles) {
+      expert = e;
+      row0 = b + (tile - before) * GM;
+      row1 = min(row0 + GM, b + n);
+      return true;
+    }
+    before += tiles;
+  }
+  return false;
+}
+
+// act[sorted row, :] = silu(a W_gate_e^T) * (a W_up_e^T) with a = x[token of the pair] (* the pair's
+// weight if scale_input).  w_gate, w_up: [experts, ff, width].
+template <typename T>
+__global__ void __launch_bounds__(256)
+experts_gate_up_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w_gate, const T* __restrict__ w_up,
+                       T* __restrict__ act, const int* __restrict__ offsets, const int* __restrict__ order,
+                       const float* __restrict__ weight, int experts, int top, int width, int ff,
+                       int scale_input) {
+  __shared__ float As[GK][GM + 4];
+  __shared__ float Gs[GK][GN + 4];
+  __shared__ float Us[GK][GN + 4];
+  int expert, row0, row1;
+  if (!find_tile(offsets, experts, blockIdx.y, expert, row0, row1)) return;
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * GN;
+  const int ty = tid >> 4, tx = tid & 15;        // 16 x 16 threads: 2 rows x 4 cols each
+  float g[2][4], u[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) g[i][j] = u[i][j] = 0.f;
+  // loaders: A 32 rows x 16 k = 512 values (2 a thread); W 64 rows x 16 k = 1024 values (4 a thread)
+  const int ar = tid >> 3, ak = (tid & 7) * 2;
+  const int wr = tid >> 2, wk = (tid & 3) * 4;
+  const int a_sorted = row0 + ar;
+  const bool a_ok = a_sorted < row1;
+  const int pair = a_ok ? order[a_sorted] : 0;
+  const float a_scale = (a_ok && scale_input) ? weight[pair] : 1.f;
+  const T* a_row = x + (size_t)(pair / top) * ldx;
+  const bool w_ok = n0 + wr < ff;
+  const T* g_row = w_gate + ((size_t)expert * ff + n0 + wr) * width;
+  const T* u_row = w_up + ((size_t)expert * ff + n0 + wr) * width;
+  for (int k0 = 0; k0 < width; k0 += GK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = k0 + ak + i;
+      As[ak + i][ar] = (a_ok && k < width) ? to_float<T>(a_row[k]) * a_scale : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + wk + i;
+      const bool ok = w_ok && k < width;
+      Gs[wk + i][wr] = ok ? to_float<T>(g_row[k]) : 0.f;
+      Us[wk + i][wr] = ok ? to_float<T>(u_row[k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GK; ++k) {
+      float a[2], bg[4], bu[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) a[i] = As[k][ty * 2 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        bg[j] = Gs[k][tx * 4 + j];
+        bu[j] = Us[k][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          g[i][j] = fmaf(a[i], bg[j], g[i][j]);
+          u[i][j] = fmaf(a[i], bu[j], u[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = row0 + ty * 2 + i;
+    if (r >= row1) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < ff) act[(size_t)r * ff + n] = from_float<T>(silu_e(round_to<T>(g[i][j])) * round_to<T>(u[i][j]));
+    }
+  }
+}
+
+// pair_out[pair of the sorted row, :] = act[sorted row, :] W_down_e^T (* the pair's weight unless
+// scale_input).  w_down: [experts, width, ff]; pair_out fp32 [pairs, width].
+template <typename T>
+__global__ void __launch_bounds__(256)
+experts_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, float* __restrict__ pair_out,
+                    const int* __restrict__ offsets, const int* __restrict__ order,
+                    const float* __restrict__ weight, int experts, int width, int ff, int scale_input) {
+  __shared__ float As[GK][GM + 4];
+  __shared__ float Ws[GK][GN + 4];
+  int expert, row0, row1;
+  if (!find_tile(offsets, experts, blockIdx.y, expert, row0, row1)) return;
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * GN;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int ar = tid >> 3, ak = (tid & 7) * 2;
+  const int wr = tid >> 2, wk = (tid & 3) * 4;
+  const bool a_ok = row0 + ar < row1;
+  const T* a_row = act + (size_t)(row0 + ar) * ff;
+  const bool w_ok = n0 + wr < width;
+  const T* w_row = w_down + ((size_t)expert * width + n0 + wr) * ff;
+  for (int k0 = 0; k0 < ff; k0 += GK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = k0 + ak + i;
+      As[ak + i][ar] = (a_ok && k < ff) ? to_float<T>(a_row[k]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + wk + i;
+      Ws[wk + i][wr] = (w_ok && k < ff) ? to_float<T>(w_row[k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GK; ++k) {
+      float a[2], b[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) a[i] = As[k][ty * 2 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = row0 + ty * 2 + i;
+    if (r >= row1) continue;
+    const int pair = order[r];
+    const float f = scale_input ? 1.f : weight[pair];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < width) pair_out[(size_t)pair * width + n] = acc[i][j] * f;
+    }
+  }
+}
+
+// hidden[t, :] += sum_j pair_out[t * top + j, :], j ascending
+__global__ void experts_combine_kernel(float* __restrict__ hidden, const float* __restrict__ pair_out,
+                                       long long total, int width, int top) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) sum += pair_out[((size_t)t * top + j) * width + c];
+    hidden[i] += sum;
+  }
+}
+
+}  // namespace leone
+
+using namespace leone;
+
+extern "C" int leone_experts_route(int dtype, const void* x, int ldx, const void* w_router, int n_tokens,
+                                   int width, int experts, int top, int softmax, int renormalize, int* chosen,
+                                   float* weight, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048) return kRefusedSize;
+  const size_t smem = sizeof(float) * 4 * (size_t)experts;
+  const dim3 grid((n_tokens + 3) / 4);
+  if (dtype == 0)
+    route_kernel<float><<<grid, 128, smem, stream>>>((const float*)x, ldx, (const float*)w_router, n_tokens, width,
+                                                     experts, top, softmax, renormalize, chosen, weight);
+  else if (dtype == 1)
+    route_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, ldx,
+                                                             (const __nv_bfloat16*)w_router, n_tokens, width,
+                                                             experts, top, softmax, renormalize, chosen, weight);
+  else
+    return kRefusedDtype;
+  return launch_result();
+}
+
+// x: [n_tokens, ldx]; chosen, weight: [n_tokens * top]; scratch: offsets int [experts + 1], order int
+// [pairs], act [pairs, ff] in the run dtype, pair_out fp32 [pairs, width]; hidden fp32 [n_tokens, width].
+extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const void* w_gate, const void* w_up,
+                                     const void* w_down, const int* chosen, const float* weight, int n_tokens,
+                                     int width, int ff, int experts, int top, int scale_input, int* offsets,
+                                     int* order, void* act, float* pair_out, float* hidden,
+                                     cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (width <= 0 || ff <= 0 || experts <= 0 || top <= 0 || experts > 8192) return kRefusedSize;
+  const long long pairs = (long long)n_tokens * top;
+  if (pairs > (1 << 30)) return kRefusedSize;
+  group_pairs_kernel<<<1, 1024, sizeof(int) * (size_t)experts, stream>>>(chosen, (int)pairs, experts, offsets, order);
+  // every expert may end with a partly filled tile
+  const long long max_tiles = (pairs + GM - 1) / GM + (experts < pairs ? experts : pairs);
+  if (max_tiles > 65535) return kRefusedSize;
+  const dim3 grid_up((ff + GN - 1) / GN, (unsigned)max_tiles), grid_down((width + GN - 1) / GN, (unsigned)max_tiles);
+  if (dtype == 0) {
+    experts_gate_up_kernel<float><<<grid_up, 256, 0, stream>>>((const float*)x, ldx, (const float*)w_gate,
+                                                               (const float*)w_up, (float*)act, offsets, order,
+                                                               weight, experts, top, width, ff, scale_input);
+    experts_down_kernel<float><<<grid_down, 256, 0, stream>>>((const float*)act, (const float*)w_down, pair_out,
+                                                              offsets, order, weight, experts, width, ff,
+                                                              scale_input);
+  } else if (dtype == 1) {
+    experts_gate_up_kernel<__nv_bfloat16><<<grid_up, 256, 0, stream>>>(
+        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up,
+        (__nv_bfloat16*)act, offsets, order, weight, experts, top, width, ff, scale_input);
+    experts_down_kernel<__nv_bfloat16><<<grid_down, 256, 0, stream>>>(
+        (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, pair_out, offsets, order, weight, experts, width,
+        ff, scale_input);
+  } else {
+    return kRefusedDtype;
+  }
+  const long long total = (long long)n_tokens * width;
+  const long long blocks = (total + 255) / 256;
+  experts_combine_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(hidden, pair_out, total,
+                                                                                              width, top);
+  return launch_result();
+}

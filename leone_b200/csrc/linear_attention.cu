@@ -1,0 +1,280 @@
+// Linear attention with a decaying state per head (no softmax):
+//
+//   S_t = decay_h * S_(t-1) + k_t v_t^T        S: [dim, vdim] fp32, per request and head
+//   o_t = S_t^T q_t
+//
+// with q, k, v = silu(their projections).  The state is read from and written back to the
+// request's state slot, so a sequence may be cut into steps anywhere: the recurrence is run token
+// by token in the same order whatever the cut, and a step of one token per sequence (decode) is
+// the same kernel.  Everything but the stored projections is fp32.
+//
+// Two forms:
+//  * `scan`: one block per (value slice, head, sequence) walks the step's tokens of its sequence
+//    in order.  The block's threads are (32 value columns) x (DP parts of the key dimension);
+//    a thread keeps its part of a state column in registers.
+//  * chunk-parallel (long prompt portions): a sequence's tokens are cut into chunks of `chunk`
+//    tokens; (1) every chunk but the last sums its own k v^T contributions from a zero state,
+//    (2) a pass over the chunks turns those into the state at each chunk's start
+//    (S_c = decay^chunk * S_(c-1) + D_(c-1)) and writes the final state's predecessor, (3) every
+//    chunk walks its tokens from its start state.  Same per-token arithmetic, 1.5 times the work,
+//    parallel over chunks.
+//
+// Then `gate_norm`: the heads of a token, concatenated, are RMS-normed together (fp32), multiplied
+// by a weight and by sigmoid(gate projection), and stored in the run dtype.
+#include "common.cuh"
+
+namespace leone {
+
+constexpr int kVS = 32;        // value columns per block
+constexpr int kTB = 8;         // tokens staged in shared memory at a time
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+// mode 0: state from `state_in` (or zero if null), outputs written, final state to `state_out` (if not null)
+// mode 1: state from zero, no outputs, final state to `state_out` (a chunk's own contribution)
+template <typename T, int DPT>
+__global__ void __launch_bounds__(256)
+linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+                             float* __restrict__ out, int ldo, float* state, float* chunk_state,
+                             const int* __restrict__ q_start, const int* __restrict__ slot_ids,
+                             const float* __restrict__ decay, int heads, int dim, int vdim,
+                             int chunk, int mode, int n_seqs, int n_slots, int* status) {
+  extern __shared__ __align__(16) float smem[];
+  const int DP = blockDim.y;
+  float* q_s = smem;                       // [kTB][dim]
+  float* k_s = q_s + kTB * dim;            // [kTB][dim]
+  float* v_s = k_s + kTB * dim;            // [kTB][kVS]
+  float* part = v_s + kTB * kVS;           // [DP][kTB][kVS]
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int tid = ty * kVS + tx, nthreads = kVS * DP;
+  const int h = blockIdx.y;
+  int s = blockIdx.z, c = 0;
+  const int v0 = blockIdx.x * kVS;
+  const int v = v0 + tx;
+  int t0, t1;
+  if (chunk > 0) {
+    // blockIdx.z counts (sequence, chunk) pairs: find this block's
+    int z = blockIdx.z, b = 0;
+    while (b < n_seqs) {
+      const int len = q_start[b + 1] - q_start[b];
+      const int nc = (len + chunk - 1) / chunk;
+      if (z < nc) break;
+      z -= nc;
+      ++b;
+    }
+    if (b >= n_seqs) return;
+    s = b;
+    c = z;
+    t0 = q_start[s] + c * chunk;
+    t1 = min(q_start[s + 1], t0 + chunk);
+    if (mode == 1 && t1 == q_start[s + 1]) return;      // the last chunk's contribution is never needed
+  } else {
+    t0 = q_start[s];
+    t1 = q_start[s + 1];
+  }
+  const int slot = slot_ids[s];
+  if (slot < 0 || slot >= n_slots) {
+    if (tid == 0) set_status(status, kBadSequence, s, slot);
+    return;
+  }
+  const float dec = decay[h];
+  const int d_per = (dim + DP - 1) / DP;
+  const int d0 = ty * d_per;
+  const size_t per_head = (size_t)dim * vdim;
+  // where this block's start state is, and where its end state goes
+  const float* s_in = nullptr;
+  float* s_out = nullptr;
+  float* slot_state = state + ((size_t)slot * heads + h) * per_head;
+  if (chunk > 0) {
+    // chunk_state: [chunk pairs][heads][dim][vdim]; an entry holds (mode 1) its chunk's own
+    // contribution, later (after the prefix pass) the state at the chunk's start
+    float* mine = chunk_state + ((size_t)blockIdx.z * heads + h) * per_head;
+    if (mode == 1) s_out = mine;
+    else {
+      s_in = mine;
+      s_out = t1 == q_start[s + 1] ? slot_state : nullptr;
+    }
+  } else {
+    s_in = slot_state;
+    s_out = slot_state;
+  }
+  float S[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = d0 + i;
+    S[i] = (s_in != nullptr && i < d_per && d < dim && v < vdim) ? s_in[(size_t)d * vdim + v] : 0.f;
+  }
+  for (int tb = t0; tb < t1; tb += kTB) {
+    const int nt = min(kTB, t1 - tb);
+    __syncthreads();
+    for (int i = tid; i < nt * dim; i += nthreads) {
+      const int tt = i / dim, d = i - tt * dim;
+      const T* row = proj + (size_t)(tb + tt) * ld + (size_t)h * dim + d;
+      q_s[tt * dim + d] = silu_f(to_float<T>(row[q_off]));
+      k_s[tt * dim + d] = silu_f(to_float<T>(row[k_off]));
+    }
+    for (int i = tid; i < nt * kVS; i += nthreads) {
+      const int tt = i / kVS, vv = i - tt * kVS;
+      v_s[i] = v0 + vv < vdim
+                   ? silu_f(to_float<T>(proj[(size_t)(tb + tt) * ld + v_off + (size_t)h * vdim + v0 + vv]))
+                   : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vt = v_s[tt * kVS + tx];
+      const float* kk = k_s + tt * dim + d0;
+      const float* qq = q_s + tt * dim + d0;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        if (i < d_per && d0 + i < dim) {
+          S[i] = fmaf(dec, S[i], kk[i] * vt);
+          acc = fmaf(S[i], qq[i], acc);
+        }
+      }
+      part[(ty * kTB + tt) * kVS + tx] = acc;
+    }
+    if (mode == 0) {
+      __syncthreads();
+      for (int i = tid; i < nt * kVS; i += nthreads) {
+        const int tt = i / kVS, vv = i - tt * kVS;
+        if (v0 + vv < vdim) {
+          float sum = 0.f;
+          for (int p = 0; p < DP; ++p) sum += part[(p * kTB + tt) * kVS + vv];
+          out[(size_t)(tb + tt) * ldo + (size_t)h * vdim + v0 + vv] = sum;
+        }
+      }
+    }
+  }
+  if (s_out != nullptr && v < vdim) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = d0 + i;
+      if (i < d_per && d < dim) s_out[(size_t)d * vdim + v] = S[i];
+    }
+  }
+}
+
+// The pass over a sequence's chunks: entry c of chunk_state holds chunk c's own contribution D_c
+// on entry and the state at chunk c's start on exit (for chunk 0 a copy of the slot's state, which
+// the last chunk overwrites while the first may still read).  One thread per state element walks
+// the chunks in order.
+__global__ void linear_attention_chunk_prefix_kernel(float* chunk_state, const float* __restrict__ state,
+                                                     const int* __restrict__ q_start,
+                                                     const int* __restrict__ slot_ids,
+                                                     const float* __restrict__ decay, int heads, int dim,
+                                                     int vdim, int chunk, int n_seqs, int n_slots) {
+  const int s = blockIdx.y;
+  const size_t per_seq = (size_t)heads * dim * vdim;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_seq) return;
+  const int slot = slot_ids[s];
+  if (slot < 0 || slot >= n_slots) return;
+  int first = 0;
+  for (int b = 0; b < s; ++b) first += (q_start[b + 1] - q_start[b] + chunk - 1) / chunk;
+  const int nc = (q_start[s + 1] - q_start[s] + chunk - 1) / chunk;
+  const int h = (int)(e / ((size_t)dim * vdim));
+  float factor = 1.f;
+  const float dec = decay[h];
+  for (int i = 0; i < chunk; ++i) factor *= dec;       // decay^chunk, as chunk multiplications
+  float run = state[(size_t)slot * per_seq + e];
+  float carry = 0.f;       // D of the chunk before
+  for (int c = 0; c < nc; ++c) {
+    float* at = chunk_state + (size_t)(first + c) * per_seq + e;
+    const float own = c + 1 < nc ? *at : 0.f;
+    if (c > 0) run = fmaf(factor, run, carry);
+    *at = run;
+    carry = own;
+  }
+}
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+gate_norm_kernel(const float* __restrict__ o, int width, const TW* __restrict__ w, const T* __restrict__ gate,
+                 int ldg, T* __restrict__ out, float eps) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const float* row = o + (size_t)t * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+  ss = block_sum(ss, scratch);
+  const float r = 1.f / sqrtf(ss / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float g = sigmoid_f(to_float<T>(gate[(size_t)t * ldg + c]));
+    out[(size_t)t * width + c] = from_float<T>(row[c] * r * to_float<TW>(w[c]) * g);
+  }
+}
+
+}  // namespace leone
+
+using namespace leone;
+
+// `proj`: [n_tokens, ld] in the run dtype with q, k (heads*dim each) and v (heads*vdim) at the given
+// column offsets.  `out`: fp32 [n_tokens, ldo], head h at columns h*vdim.  `state`: fp32
+// [n_slots, heads, dim, vdim].  chunk == 0: the walk in order; chunk > 0: the chunk-parallel form
+// with `n_chunks` = sum over sequences of ceil(len / chunk) and `chunk_state` fp32
+// [n_chunks, heads, dim, vdim].
+extern "C" int leone_linear_attention(int dtype, const void* proj, int ld, int q_off, int k_off, int v_off,
+                                      float* out, int ldo, float* state, const int* q_start,
+                                      const int* slot_ids, const float* decay, int n_seqs, int heads,
+                                      int dim, int vdim, int n_slots, int chunk, int n_chunks,
+                                      float* chunk_state, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || n_seqs > 65535 || dim > 512) return kRefusedSize;
+  if (chunk < 0 || (chunk > 0 && (n_chunks <= 0 || n_chunks > 65535 || chunk_state == nullptr))) return kRefusedSize;
+  int dp = 4, dpt;
+  if (dim > 256) dp = 8;
+  const int d_per = (dim + dp - 1) / dp;
+  dpt = d_per <= 8 ? 8 : d_per <= 16 ? 16 : d_per <= 32 ? 32 : 64;
+  const dim3 block(kVS, dp);
+  const size_t smem = sizeof(float) * ((size_t)2 * kTB * dim + kTB * kVS + (size_t)dp * kTB * kVS);
+  const int vslices = (vdim + kVS - 1) / kVS;
+#define SCAN(T, D, GRIDZ, MODE)                                                                            \
+  linear_attention_scan_kernel<T, D><<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(                  \
+      (const T*)proj, ld, q_off, k_off, v_off, out, ldo, state, chunk_state, q_start, slot_ids, decay,     \
+      heads, dim, vdim, chunk, MODE, n_seqs, n_slots, status)
+#define SCAN_D(T, GRIDZ, MODE)                          \
+  do {                                                  \
+    if (dpt == 8) SCAN(T, 8, GRIDZ, MODE);              \
+    else if (dpt == 16) SCAN(T, 16, GRIDZ, MODE);       \
+    else if (dpt == 32) SCAN(T, 32, GRIDZ, MODE);       \
+    else SCAN(T, 64, GRIDZ, MODE);                      \
+  } while (0)
+#define SCAN_T(GRIDZ, MODE)                             \
+  do {                                                  \
+    if (dtype == 0) SCAN_D(float, GRIDZ, MODE);         \
+    else SCAN_D(__nv_bfloat16, GRIDZ, MODE);            \
+  } while (0)
+  if (dtype != 0 && dtype != 1) return kRefusedDtype;
+  if (chunk == 0) {
+    SCAN_T(n_seqs, 0);
+    return launch_result();
+  }
+  SCAN_T(n_chunks, 1);
+  const size_t per_seq = (size_t)heads * dim * vdim;
+  linear_attention_chunk_prefix_kernel<<<dim3((unsigned)((per_seq + 255) / 256), n_seqs), 256, 0, stream>>>(
+      chunk_state, state, q_start, slot_ids, decay, heads, dim, vdim, chunk, n_seqs, n_slots);
+  SCAN_T(n_chunks, 0);
+#undef SCAN_T
+#undef SCAN_D
+#undef SCAN
+  return launch_result();
+}
+
+// out[t, c] = o[t, c] / sqrt(mean_c(o[t, :]^2) + eps) * w[c] * sigmoid(gate[t, c]); o fp32, out and
+// gate in the run dtype (gate rows `ldg` apart), w in `w_dtype`.
+extern "C" int leone_gate_norm(int dtype, const float* o, int n_tokens, int width, const void* w, int w_dtype,
+                               const void* gate, int ldg, void* out, float eps, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (width <= 0) return kRefusedSize;
+#define GN(T, TW) \
+  gate_norm_kernel<T, TW><<<n_tokens, 256, 0, stream>>>(o, width, (const TW*)w, (const T*)gate, ldg, (T*)out, eps)
+  if (dtype == 0 && w_dtype == 0) GN(float, float);
+  else if (dtype == 1 && w_dtype == 0) GN(__nv_bfloat16, float);
+  else if (dtype == 1 && w_dtype == 1) GN(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == 0 && w_dtype == 1) GN(float, __nv_bfloat16);
+  else return kRefusedDtype;
+#undef GN
+  return launch_result();
+}

@@ -360,6 +360,154 @@ class CudaOps:
             c_float(scale), int(window or 0), cache.page_tokens, kp.shape[0], bt.shape[0],
             _ptr(ctx.status), self._stream()), "attention_generic")
 
+    # -- mixers and feed-forwards of the 'mixers' module (compiled when a model first needs it) ----
+    @property
+    def mixers(self):
+        lib = self.__dict__.get("_mixers")
+        if lib is None:
+            lib = self.__dict__["_mixers"] = ctypes.CDLL(ensure_built("mixers"))
+        return lib
+
+    def rms_norm_pair(self, x, w_a, w_b, out_a, out_b, eps):
+        """Two RMS norms (weights ``w_a``, ``w_b``, one eps) of the same fp32 rows in one pass."""
+        n, width = out_a.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape == (n, width), "rms_norm_pair input")
+        _need(out_b.shape == out_a.shape and out_a.dtype == out_b.dtype and out_a.is_contiguous()
+              and out_b.is_contiguous() and w_a.dtype == w_b.dtype and w_a.numel() == width == w_b.numel(),
+              "rms_norm_pair outputs/weights")
+        self.launches += 1
+        _check(self.mixers.leone_rms_norm_pair(_ptr(x), _ptr(w_a), _ptr(w_b), _dt(w_a.dtype), _ptr(out_a), _ptr(out_b),
+                                               _dt(out_a.dtype), n, width, c_float(eps), self._stream()), "rms_norm_pair")
+
+    def relu_squared(self, t):
+        """In place: ``max(t, 0)^2``."""
+        _need(t.is_contiguous(), "relu_squared needs a contiguous tensor")
+        self.launches += 1
+        _check(self.mixers.leone_relu_squared(_dt(t.dtype), _ptr(t), ctypes.c_longlong(t.numel()), self._stream()),
+               "relu_squared")
+
+    def linear_per_head(self, a, a_head_stride, w, c, c_head_stride, heads, k, n):
+        """``c[t, h*c_head_stride : +n] = a[t, h*a_head_stride : +k] @ w[h].T`` for every head;
+        ``w``: ``[heads, n, k]`` contiguous."""
+        m = a.shape[0]
+        _need(c.shape[0] == m and a.dtype == c.dtype == w.dtype and a.stride(1) == 1 and c.stride(1) == 1
+              and w.is_contiguous() and tuple(w.shape) == (heads, n, k), "linear_per_head layout")
+        _need((heads - 1) * a_head_stride + k <= a.shape[1] and (heads - 1) * c_head_stride + n <= c.shape[1],
+              "linear_per_head: heads run past a row")
+        self.launches += 1
+        _check(self.mixers.leone_gemm_batched(_dt(a.dtype), _ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), k,
+                                              c.stride(0), ctypes.c_longlong(a_head_stride),
+                                              ctypes.c_longlong(n * k), ctypes.c_longlong(c_head_stride), heads,
+                                              self._stream()), "linear_per_head")
+
+    def linear_attention(self, ctx, proj, out, state, decay, heads, dim, vdim, q_off, k_off, v_off, chunk=0):
+        """The decaying-state recurrence over the step's tokens (``csrc/linear_attention.cu``).
+        ``chunk`` > 0: prompt portions are cut into chunks of that many tokens that run side by side."""
+        n = proj.shape[0]
+        _need(proj.stride(1) == 1 and out.dtype == torch.float32 and out.is_contiguous()
+              and out.shape == (n, heads * vdim), "linear_attention layout")
+        _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+              and decay.dtype == torch.float32 and decay.numel() == heads, "linear_attention state/decay")
+        n_chunks, chunk_state = 0, None
+        if chunk > 0:
+            n_chunks = int(sum(-(-int(q) // chunk) for q in ctx.q_lens))
+            chunk_state = self._scratch("linattn_chunks", n_chunks, heads * dim * vdim, torch.float32)
+        self.launches += 1 if chunk == 0 else 3
+        _check(self.mixers.leone_linear_attention(
+            _dt(proj.dtype), _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(out), out.stride(0), _ptr(state),
+            _ptr(ctx.q_start), _ptr(ctx.slot_ids), _ptr(decay), ctx.n_seqs, heads, dim, vdim, state.shape[0], chunk,
+            n_chunks, _ptr(chunk_state), _ptr(ctx.status), self._stream()), "linear_attention")
+
+    def gate_norm(self, o, weight, gate, out, eps):
+        """``out = rms_norm(o) * weight * sigmoid(gate)``; ``o`` fp32, ``gate`` a column slice."""
+        n, width = o.shape
+        _need(o.dtype == torch.float32 and o.is_contiguous() and out.shape == o.shape and out.is_contiguous()
+              and gate.shape == o.shape and gate.stride(1) == 1 and gate.dtype == out.dtype
+              and weight.numel() == width, "gate_norm layout")
+        self.launches += 1
+        _check(self.mixers.leone_gate_norm(_dt(out.dtype), _ptr(o), n, width, _ptr(weight), _dt(weight.dtype), _ptr(gate),
+                                           gate.stride(0), _ptr(out), c_float(eps), self._stream()), "gate_norm")
+
+    def latent_prepare(self, ctx, proj, q_abs, heads, dim, rot_dim, rank, norm_w, eps, freqs, magnitude, pairing,
+                       cache, q_off, dkv_off):
+        """Cache rows [normed latent | rotated shared key part] of the step's tokens and the
+        rotated query parts (``csrc/attention_latent.cu``).  ``freqs``: fp32 per pair, or None."""
+        n = proj.shape[0]
+        dk = rank + rot_dim
+        _need(proj.stride(1) == 1 and q_abs.is_contiguous() and q_abs.shape == (n, heads * dk)
+              and q_abs.dtype == proj.dtype and norm_w.numel() == rank, "latent_prepare layout")
+        rot_dims = 0
+        if freqs is not None:
+            _need(freqs.dtype == torch.float32 and freqs.is_contiguous(), "latent_prepare frequencies")
+            rot_dims = 2 * freqs.numel()
+        if cache is not None:
+            kp, bt = cache.k_pool, cache.block_table
+            _need(cache.v_pool is None and kp.is_contiguous() and kp.dtype == proj.dtype and kp.shape[1] == 1
+                  and kp.shape[2] == cache.page_tokens and kp.shape[3] == dk and bt.dtype == torch.int32
+                  and bt.is_contiguous(), "latent cache layout")
+            pool_args = (_ptr(bt), bt.shape[1], bt.shape[0], _ptr(kp), kp.shape[0], cache.page_tokens)
+        else:
+            pool_args = (c_void_p(0), 0, ctx.n_seqs, c_void_p(0), 0, 0)
+        self.launches += 1
+        _check(self.mixers.leone_latent_prepare(
+            _dt(proj.dtype), _ptr(proj), proj.stride(0), q_off, dkv_off, _ptr(q_abs), n, heads, dim, rot_dim, rank,
+            _ptr(norm_w), _dt(norm_w.dtype), c_float(eps), _ptr(freqs), rot_dims, c_float(magnitude),
+            1 if pairing == "adjacent" else 0, _ptr(ctx.positions), _ptr(ctx.seq_of_token), pool_args[0],
+            pool_args[1], pool_args[2], pool_args[3], pool_args[4], pool_args[5], _ptr(ctx.status), self._stream()),
+            "latent_prepare")
+
+    def attention_latent(self, ctx, q_abs, out, cache, heads, dk, dv, scale, window, sink=None, gate=None):
+        """Softmax attention of ``q_abs [n, heads*dk]`` over cache rows of ``dk`` elements whose
+        first ``dv`` are the value; ``sink``: per head or None; ``gate``: ``[n, >= heads]`` or None."""
+        n = q_abs.shape[0]
+        kp, bt = cache.k_pool, cache.block_table
+        _need(q_abs.is_contiguous() and out.is_contiguous() and out.shape == (n, heads * dv) and out.dtype == q_abs.dtype
+              and kp.dtype == q_abs.dtype and kp.is_contiguous() and kp.shape[3] == dk and kp.shape[1] == 1,
+              "attention_latent layout")
+        if gate is not None:
+            _need(gate.dtype == q_abs.dtype and gate.stride(1) == 1 and gate.shape[0] == n and gate.shape[1] >= heads,
+                  "attention_latent gate")
+        if sink is not None:
+            _need(sink.numel() == heads and sink.is_contiguous(), "attention_latent sink")
+        self.launches += 1
+        _check(self.mixers.leone_attention_latent(
+            _dt(q_abs.dtype), _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token),
+            _ptr(ctx.positions), n, heads, dk, dv, c_float(scale), int(window or 0), _ptr(sink),
+            0 if sink is None else _dt(sink.dtype), _ptr(gate), 0 if gate is None else gate.stride(0),
+            cache.page_tokens, kp.shape[0], bt.shape[0], _ptr(ctx.status), self._stream()), "attention_latent")
+
+    def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False):
+        """Router scores in fp32 and the ``top`` best experts of every token (``csrc/experts.cu``)."""
+        n, width = x.shape
+        experts = w_router.shape[0]
+        _need(x.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == width and w_router.dtype == x.dtype
+              and chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top
+              and weight.numel() == n * top, "experts_route layout")
+        self.launches += 1
+        _check(self.mixers.leone_experts_route(_dt(x.dtype), _ptr(x), x.stride(0), _ptr(w_router), n, width, experts, top,
+                                               1 if softmax else 0, 1 if renormalize else 0, _ptr(chosen), _ptr(weight),
+                                               self._stream()), "experts_route")
+
+    def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
+        """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``."""
+        n, width = x.shape
+        experts, ff = w_gate.shape[0], w_gate.shape[1]
+        _need(x.stride(1) == 1 and w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+              and tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff)
+              and w_gate.dtype == x.dtype and hidden.dtype == torch.float32 and hidden.is_contiguous()
+              and hidden.shape == (n, width), "experts_forward layout")
+        pairs = n * top
+        cap = rt.max_tokens * top
+        offsets = rt.flat_buffer("experts_offsets", experts + 1, torch.int32)
+        order = rt.flat_buffer("experts_order", pairs, torch.int32, reserve=cap)
+        act = rt.flat_buffer("experts_act", pairs * ff, x.dtype, reserve=cap * ff)
+        pair_out = rt.flat_buffer("experts_pair_out", pairs * width, torch.float32, reserve=cap * width)
+        self.launches += 4
+        _check(self.mixers.leone_experts_forward(
+            _dt(x.dtype), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(chosen), _ptr(weight), n,
+            width, ff, experts, top, 1 if scale_input else 0, _ptr(offsets), _ptr(order), _ptr(act), _ptr(pair_out),
+            _ptr(hidden), self._stream()), "experts_forward")
+
     def sample(self, logits, temperature, seeds, positions, out):
         rows, vocab = logits.shape
         _need(logits.dtype == torch.float32 and logits.is_contiguous(), "logits must be fp32")

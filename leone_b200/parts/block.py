@@ -42,3 +42,31 @@ class PreNormBlock(Block):
         else:
             self.feed_forward.forward(ctx, x, hidden)
         return after if after is not None and after.ready else None
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """``h <- h + mixer(norm_a(h)) + ffn(norm_b(h))``: both branches read the same ``h``, each
+    through a norm of its own.  Both norms are made before either branch adds to the residual
+    stream (in one pass over the rows where the kernels offer it: the two share the rows' mean
+    square when they are RMS norms with one eps).  A layer without a feed-forward has the mixer
+    branch only."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, **extra):
+        if mixer_norm is None or (feed_forward is None) != (ffn_norm is None) or extra:
+            raise ValueError("the parallel arrangement is a mixer with its norm and, optionally, a feed-forward with its")
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm)
+
+    def forward(self, ctx, cache, hidden):
+        a, b = self.mixer_norm, self.ffn_norm
+        if b is None:
+            self.mixer.forward(ctx, cache, a.forward(ctx, hidden), hidden)
+            return
+        pair = getattr(a, "forward_pair", None)
+        if pair is not None and type(a) is type(b) and getattr(a, "eps", None) == getattr(b, "eps", 0):
+            xa, xb = pair(ctx, hidden, b)
+        else:
+            xa = a.forward(ctx, hidden)
+            xb = b.forward(ctx, hidden, out_name="normed_b")
+        self.mixer.forward(ctx, cache, xa, hidden)
+        self.feed_forward.forward(ctx, xb, hidden)

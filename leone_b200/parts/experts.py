@@ -1,0 +1,98 @@
+"""Mixture of experts: each token runs through its ``top`` best-scoring small gated layers.
+
+Router logits ``z = W_router x`` and scores in fp32: ``score = "sigmoid"`` (each expert's own
+``sigmoid(z_e)``) or ``"softmax"``; the ``top`` largest are chosen (the lowest index among equal
+scores) and weigh their experts, as they are or divided by their sum (``renormalize``).  The weight
+multiplies the expert's input (``scale = "input"``: ``sum expert_e(w_e x)``) or its output
+(``"output"``).  An expert is ``W_down (silu(W_gate a) * (W_up a))`` without biases.  An optional
+shared expert of the same form (size ``shared_size``) runs on every token and is added.
+
+Experts' matrices are stacked at load time (``[experts, ff, hidden]`` twice and ``[experts, hidden,
+ff]``); the pairs (token, choice) are grouped by expert on the device and the grouped products run
+over them, so nothing is read back by the host and a captured decode step can replay it.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..registry import FEED_FORWARDS
+from .base import FeedForward, WeightSpec
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, params, rt):
+        super().__init__(params, rt)
+        self.hidden = int(params["hidden_size"])
+        self.ff = int(params["expert_size"])
+        self.experts = int(params["num_experts"])
+        self.top = int(params["top"])
+        self.score = params.get("score", "sigmoid")
+        self.renormalize = bool(params.get("renormalize", False))
+        self.scale = params.get("scale", "input")
+        shared = params.get("shared_size")
+        self.shared_ff = int(shared) if shared else None
+        if self.score not in ("sigmoid", "softmax") or self.scale not in ("input", "output"):
+            raise ValueError(f"routed experts: score '{self.score}' / scale '{self.scale}'")
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"routed experts: top {self.top} of {self.experts}")
+        self.router_name = params.get("router_name", "router")
+        self.expert_pattern = params.get("expert_pattern", "e{}.{}")      # (index, gate|up|down)
+        self.shared_pattern = params.get("shared_pattern", "shared.{}")
+        self.w_router = self.w_gate = self.w_up = self.w_down = self.w_shared_gate_up = self.w_shared_down = None
+
+    def _expert(self, e, which):
+        return self.expert_pattern.format(e, which)
+
+    def weight_specs(self):
+        specs = []
+        for e in range(self.experts):
+            specs += [WeightSpec(self._expert(e, "gate"), (self.ff, self.hidden)),
+                      WeightSpec(self._expert(e, "up"), (self.ff, self.hidden)),
+                      WeightSpec(self._expert(e, "down"), (self.hidden, self.ff))]
+        specs.append(WeightSpec(self.router_name, (self.experts, self.hidden)))
+        if self.shared_ff:
+            specs += [WeightSpec(self.shared_pattern.format("gate"), (self.shared_ff, self.hidden)),
+                      WeightSpec(self.shared_pattern.format("up"), (self.shared_ff, self.hidden)),
+                      WeightSpec(self.shared_pattern.format("down"), (self.hidden, self.shared_ff))]
+        return specs
+
+    def load(self, tensors):
+        def stack(which):
+            return torch.stack([tensors[self._expert(e, which)] for e in range(self.experts)]).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.w_router = tensors[self.router_name].contiguous()
+        if self.shared_ff:
+            ops = self.rt.ops
+            self.w_shared_gate_up = ops.prepare_gate_up(tensors[self.shared_pattern.format("gate")],
+                                                        tensors[self.shared_pattern.format("up")])
+            self.w_shared_down = ops.prepare_matrix(tensors[self.shared_pattern.format("down")])
+
+    def weight_bytes(self):
+        # a decode step reads the router, the shared expert and `top` experts per token (at most all)
+        per_expert = 3 * self.ff * self.hidden
+        return (self.experts * self.hidden + 3 * (self.shared_ff or 0) * self.hidden
+                + self.top * per_expert) * self.rt.dtype.itemsize
+
+    def scratch_bytes(self, max_tokens):
+        pairs = max_tokens * self.top
+        item = self.rt.dtype.itemsize
+        return pairs * (8 + self.ff * item + self.hidden * 4) + 4 * (self.experts + 1 + pairs) \
+            + max_tokens * 3 * (self.shared_ff or 0) * item
+
+    def load_transient_bytes(self):
+        return 3 * self.experts * self.ff * self.hidden * self.rt.dtype.itemsize
+
+    def forward(self, ctx, x, hidden):
+        rt, ops = self.rt, self.rt.ops
+        n = hidden.shape[0]
+        pairs = n * self.top
+        chosen = rt.flat_buffer("experts_chosen", pairs, torch.int32, reserve=rt.max_tokens * self.top)[:pairs]
+        weight = rt.flat_buffer("experts_weight", pairs, torch.float32, reserve=rt.max_tokens * self.top)[:pairs]
+        ops.experts_route(x, self.w_router, chosen, weight, self.top, self.score == "softmax", self.renormalize)
+        ops.experts_forward(x, self.w_gate, self.w_up, self.w_down, chosen, weight, self.top,
+                            self.scale == "input", hidden, rt)
+        if self.shared_ff:
+            act = rt.buffer("experts_shared_act", n, self.shared_ff, rt.dtype)
+            ops.linear_swiglu(x, self.w_shared_gate_up, act)
+            ops.linear(act, self.w_shared_down, hidden, residual=hidden)

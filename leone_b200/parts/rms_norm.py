@@ -35,3 +35,11 @@ class RMSNorm(Norm):
         out = self.rt.buffer(out_name, n, self.size, self.rt.dtype)
         self.rt.ops.rms_norm(hidden, self.weight, out, self.eps, rows)
         return out
+
+    def forward_pair(self, ctx, hidden, other: "RMSNorm"):
+        """This norm and ``other`` (same size and eps) of the same rows in one pass."""
+        n = hidden.shape[0]
+        out_a = self.rt.buffer("normed", n, self.size, self.rt.dtype)
+        out_b = self.rt.buffer("normed_b", n, self.size, self.rt.dtype)
+        self.rt.ops.rms_norm_pair(hidden, self.weight, other.weight, out_a, out_b, self.eps)
+        return out_a, out_b

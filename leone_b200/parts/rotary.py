@@ -53,3 +53,63 @@ class RotaryAdjacent(RotaryHalfSplit):
     """The same angles with pair ``i`` made of elements ``(2i, 2i + 1)``: the table is the same,
     the kernels are told which elements belong together."""
     pairing = "adjacent"
+
+
+def scaled_frequencies(dims: int, base: float, scaling=None):
+    """Per pair ``i`` the frequency ``f_i = base^(-2i/dims)``, blended by YaRN if ``scaling``
+    (a mapping with ``factor``, ``original``, ``fast``, ``slow``) is given, and the factor that
+    multiplies cos and sin.
+
+    YaRN (Peng et al., "YaRN: Efficient Context Window Extension of Large Language Models"): a
+    pair that turns more than ``fast`` times within ``original`` positions keeps its frequency,
+    one that turns fewer than ``slow`` times has it divided by ``factor``, and those between are
+    blended linearly in the pair index: with ``idx(t) = dims * ln(original / (2 pi t)) / (2 ln
+    base)``, ``lo = max(floor(idx(fast)), 0)``, ``hi = min(ceil(idx(slow)), dims - 1)`` and
+    ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency is ``f_i / factor *
+    ramp_i + f_i * (1 - ramp_i)``; cos and sin are multiplied by ``0.1 ln(factor) + 1``."""
+    import math
+    half = dims // 2
+    freqs = [float(base) ** (-2.0 * i / dims) for i in range(half)]
+    if not scaling:
+        return freqs, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def idx(turns):
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+    lo = max(math.floor(idx(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(idx(float(scaling["slow"]))), dims - 1)
+    span = max(hi - lo, 0.001)
+    out = []
+    for i, f in enumerate(freqs):
+        ramp = min(max((i - lo) / span, 0.0), 1.0)
+        out.append(f / factor * ramp + f * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+@POSITION_ENCODINGS.register("rotary_computed")
+class RotaryComputed(PositionEncoding):
+    """A rotary encoding without a table and so without a limit on positions: it offers its
+    per-pair frequencies (fp32) and a magnitude, and the kernel that applies it forms the angle
+    ``position * frequency`` and its cos and sin in fp32 itself.  ``scaling``: YaRN constants or
+    ``None``.  ``pairing``: ``"adjacent"`` (pair i = elements 2i, 2i+1) or ``"half_split"``."""
+
+    def __init__(self, params, rt):
+        super().__init__(params, rt)
+        self.rotary_dim = int(params["rotary_dim"])
+        self.base = float(params["base"])
+        self.scaling = params.get("scaling")
+        self.pairing = params.get("pairing", "adjacent")
+        if self.rotary_dim % 2 or self.rotary_dim <= 0:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and positive")
+        if self.pairing not in ("adjacent", "half_split"):
+            raise ValueError(f"rotary pairing '{self.pairing}'")
+        freqs, self.magnitude = scaled_frequencies(self.rotary_dim, self.base, self.scaling)
+        self._freqs_host = torch.tensor(freqs, dtype=torch.float64).to(torch.float32)
+        self._freqs = None
+
+    def frequencies(self):
+        """fp32 ``[rotary_dim / 2]`` on the device."""
+        if self._freqs is None:
+            self._freqs = self._freqs_host.to(self.rt.device)
+        return self._freqs

@@ -125,6 +125,116 @@ class EmulatedOps:
                 res[t, h] = (w[:, None] * vals[:, h // g, :]).sum(0)
         out.copy_(res.reshape(n, n_q * d).to(out.dtype))
 
+    # -- stand-ins for the kernels of the 'mixers' module ----------------------------------------
+    def rms_norm_pair(self, x, w_a, w_b, out_a, out_b, eps):
+        self.rms_norm(x, w_a, out_a, eps)
+        self.rms_norm(x, w_b, out_b, eps)
+
+    def relu_squared(self, t):
+        t.copy_((torch.relu(t.float()) ** 2).to(t.dtype))
+
+    def linear_per_head(self, a, a_head_stride, w, c, c_head_stride, heads, k, n):
+        for h in range(heads):
+            c[:, h * c_head_stride:h * c_head_stride + n] = \
+                (a[:, h * a_head_stride:h * a_head_stride + k].float() @ w[h].float().t()).to(c.dtype)
+
+    def linear_attention(self, ctx, proj, out, state, decay, heads, dim, vdim, q_off, k_off, v_off, chunk=0):
+        silu = torch.nn.functional.silu
+        p = proj.float()
+        bounds, slots = ctx.q_start.tolist(), ctx.slot_ids.tolist()
+        for s, slot in enumerate(slots):
+            st = state[slot]
+            for t in range(bounds[s], bounds[s + 1]):
+                q = silu(p[t, q_off:q_off + heads * dim]).view(heads, dim)
+                k = silu(p[t, k_off:k_off + heads * dim]).view(heads, dim)
+                v = silu(p[t, v_off:v_off + heads * vdim]).view(heads, vdim)
+                st = decay[:, None, None] * st + k[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", st, q).reshape(-1)
+            state[slot] = st
+
+    def gate_norm(self, o, weight, gate, out, eps):
+        r = torch.rsqrt((o * o).mean(dim=-1, keepdim=True) + eps)
+        out.copy_((o * r * weight.float() * torch.sigmoid(gate.float())).to(out.dtype))
+
+    @staticmethod
+    def _rotate(x, pos, freqs, magnitude, pairing):
+        if freqs is None:
+            return x
+        ang = pos.float()[:, None] * freqs[None, :]
+        cos, sin = torch.cos(ang) * magnitude, torch.sin(ang) * magnitude
+        while cos.dim() < x.dim():
+            cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+        rd = 2 * freqs.numel()
+        out = x.clone()
+        if pairing == "adjacent":
+            u, v = x[..., 0:rd:2], x[..., 1:rd:2]
+            out[..., 0:rd:2], out[..., 1:rd:2] = u * cos - v * sin, v * cos + u * sin
+        else:
+            u, v = x[..., :rd // 2], x[..., rd // 2:rd]
+            out[..., :rd // 2], out[..., rd // 2:rd] = u * cos - v * sin, v * cos + u * sin
+        return out
+
+    def latent_prepare(self, ctx, proj, q_abs, heads, dim, rot_dim, rank, norm_w, eps, freqs, magnitude, pairing,
+                       cache, q_off, dkv_off):
+        n = proj.shape[0]
+        p = proj.float()
+        pos = ctx.positions.long()
+        q = p[:, q_off:q_off + heads * (dim + rot_dim)].view(n, heads, dim + rot_dim)
+        q_abs.view(n, heads, rank + rot_dim)[:, :, rank:] = \
+            self._rotate(q[:, :, dim:], pos, freqs, magnitude, pairing).to(q_abs.dtype)
+        if cache is None:
+            return
+        dkv = p[:, dkv_off:dkv_off + rank + rot_dim]
+        c = dkv[:, :rank]
+        c = c * torch.rsqrt((c * c).mean(dim=-1, keepdim=True) + eps) * norm_w.float()
+        r = self._rotate(dkv[:, rank:], pos, freqs, magnitude, pairing)
+        pt = cache.page_tokens
+        page = cache.block_table[ctx.seq_of_token.long(), pos // pt].long()
+        assert (page >= 0).all(), "write into a block without a page"
+        cache.k_pool[page, 0, pos % pt, :] = torch.cat([c, r], dim=-1).to(cache.k_pool.dtype)
+
+    def attention_latent(self, ctx, q_abs, out, cache, heads, dk, dv, scale, window, sink=None, gate=None):
+        n = q_abs.shape[0]
+        q = q_abs.float().view(n, heads, dk)
+        pt = cache.page_tokens
+        res = torch.zeros(n, heads, dv)
+        positions, seqs = ctx.positions.tolist(), ctx.seq_of_token.tolist()
+        for t in range(n):
+            p, s = positions[t], seqs[t]
+            lo = 0 if not window else max(0, p - window + 1)
+            idx = torch.arange(lo, p + 1)
+            pages = cache.block_table[s, idx // pt].long()
+            assert (pages >= 0).all(), "read from a block without a page"
+            rows = cache.k_pool[pages, 0, idx % pt, :].float()
+            sc = (rows @ q[t].t()) * scale                       # [keys, heads]
+            if sink is not None:
+                sc = torch.cat([sc, sink.float()[None, :]], dim=0)
+            w = torch.softmax(sc, dim=0)[:rows.shape[0]]
+            res[t] = w.t() @ rows[:, :dv]
+            if gate is not None:
+                res[t] *= torch.sigmoid(gate[t, :heads].float())[:, None]
+        out.copy_(res.reshape(n, heads * dv).to(out.dtype))
+
+    def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False):
+        z = x.float() @ w_router.float().t()
+        s = torch.softmax(z, dim=-1) if softmax else torch.sigmoid(z)
+        val, idx = torch.topk(s, top, dim=-1)
+        if renormalize:
+            val = val / val.sum(dim=-1, keepdim=True)
+        chosen.copy_(idx.reshape(-1).to(torch.int32))
+        weight.copy_(val.reshape(-1))
+
+    def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
+        n = x.shape[0]
+        silu = torch.nn.functional.silu
+        xf = x.float()
+        for t in range(n):
+            for j in range(top):
+                e, w = int(chosen[t * top + j]), weight[t * top + j]
+                a = xf[t] * w if scale_input else xf[t]
+                y = w_down[e].float() @ (silu(w_gate[e].float() @ a) * (w_up[e].float() @ a))
+                hidden[t] += y if scale_input else y * w
+
     def sample(self, logits, temperature, seeds, positions, out):
         from tests.plain.model import sample
         for i in range(logits.shape[0]):
