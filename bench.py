@@ -6,7 +6,8 @@
 Prints one JSON line.  ``--gpus N`` with N > 1 prints one line saying that this engine runs
 on one GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
 ``--shape qwen3-32b | qwen3-1.7b``, ``--batch``, ``--context`` measure the other baseline
-configurations; ``--workload serving`` runs many requests through the scheduler.
+configurations; ``--workload serving`` runs many requests through the scheduler; ``--design sarizen``
+measures that design beside the dense decoder at equal size.
 """
 import argparse
 import os
@@ -32,10 +33,18 @@ def main() -> int:
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
                     help="serving: many requests with mixed prompt lengths through the scheduler (its own JSON line)")
     ap.add_argument("--requests", type=int, default=64, help="serving: concurrent requests")
+    ap.add_argument("--design", default=None, choices=["sarizen"],
+                    help="another design at layer sizes like a real model's beside the dense decoder at equal "
+                         "size: prefill and decode tokens/s and time per kind of kernel (its own JSON line)")
+    ap.add_argument("--size", default="small", choices=["small", "medium"], help="--design: which layer sizes")
     args = ap.parse_args()
     if args.impl != "reference" and args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.design and args.impl != "reference":
+        from leone_b200.benchmark import compare_designs
+        return compare_designs(args.design, args.size, steps=min(args.steps, 64), warmup=max(args.warmup, 3),
+                               batch=args.batch, context=args.context or 2048)
     if args.workload == "serving" and args.impl != "reference":
         from leone_b200.benchmark import serving
         return serving(args.shape or "qwen3-1.7b", requests=args.requests, layers=args.layers)

@@ -140,11 +140,14 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, seed:
     last = engine.decode_steps(rids, last, params, max(warmup, 1))[-1]
     times = []
     mid = []
+    # fixed-size state cannot be rewound, nor a window group whose pages went back: such models decode on
+    rewind = not engine._run_state and all(g.spec.kind == "full" for g in engine.cache.groups)
     for _ in range(reps):
         # every run starts from the same context length: the tokens of the run before are dropped
         engine.drop_lookahead()
         for r in rids:
-            engine.cache.truncate(r, context + max(warmup, 1))
+            if rewind:
+                engine.cache.truncate(r, context + max(warmup, 1))
         mid.append(engine.cache.length(rids[0]) + steps / 2.0)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -363,4 +366,151 @@ def run(gpus: int, steps: int, warmup: int, impl: str, layers: Optional[int] = N
         "roofline": roofline, "points": extra, "impl": "leone_b200", "build_seconds": round(build_s, 1),
     }
     print(json.dumps(line))
+    return 0
+
+
+# -- another design beside its closest existing model -------------------------------------------
+def _sarizen_shape(width: int, layers: int, heads: int, experts: int, top: int, expert_ff: int, shared_ff: int,
+                   kv_rank: int, window: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: one latent-attention layer (dense feed-forward if it is
+    the first) to every three lightning layers, routed experts elsewhere."""
+    decay = [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(heads - 1, 1)) for h in range(heads)]
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": kv_rank, "scale": 192 ** -0.5,
+              "mask": {"size": window},
+              "rot": {"base": 10000.0, "dims": 64,
+                      "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    lightning = {"heads": heads, "dim": 128, "vdim": 128, "decay": decay}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": shared_ff}}
+    out = []
+    for i in range(layers):
+        attn = i % 4 == 0
+        out.append({"type": "latent_attention" if attn else "lightning", "mixer": latent if attn else lightning,
+                    "mlp": {"kind": "dense", "ff": top * expert_ff + shared_ff} if i == 0 else moe})
+    return {"architecture": "Sarizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": out}
+
+
+DESIGN_SIZES = {
+    # name: (width, layers, heads, experts, top, expert ff, shared ff, kv rank, window, vocab)
+    "small": (2048, 8, 16, 32, 4, 512, 1024, 512, 1024, 32768),
+    "medium": (4096, 8, 32, 64, 6, 1024, 2048, 512, 2048, 65536),
+}
+
+
+class _OpTimer:
+    """Wraps the kernel table's calls with CUDA events: device time per kind of call."""
+
+    def __init__(self, ops):
+        self.ops = ops
+        self.records = []
+        self._orig = {}
+
+    def __enter__(self):
+        names = ["linear", "linear_swiglu", "rms_norm", "rms_norm_pair", "relu_squared", "linear_per_head",
+                 "linear_attention", "gate_norm", "latent_prepare", "attention_latent", "experts_route",
+                 "experts_forward", "attention", "qk_norm_rope_write", "embedding", "logit_post"]
+        for name in names:
+            fn = getattr(self.ops, name, None)
+            if fn is None:
+                continue
+            self._orig[name] = fn
+
+            def timed(*a, _fn=fn, _name=name, **kw):
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                r = _fn(*a, **kw)
+                stop.record()
+                label = _name
+                if _name in ("linear", "linear_swiglu"):
+                    w = a[1]
+                    label = f"{_name} {tuple(w.shape)[0]}x{tuple(w.shape)[1]}"
+                self.records.append((label, start, stop))
+                return r
+            setattr(self.ops, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        for name in self._orig:
+            try:
+                delattr(self.ops, name)
+            except AttributeError:
+                pass
+        return False
+
+    def table(self) -> Dict[str, dict]:
+        torch.cuda.synchronize()
+        out: Dict[str, dict] = {}
+        for label, start, stop in self.records:
+            e = out.setdefault(label, {"calls": 0, "ms": 0.0})
+            e["calls"] += 1
+            e["ms"] += start.elapsed_time(stop)
+        return out
+
+
+def _op_times(engine, tokens: int, batch: int, context: int) -> dict:
+    """Device time per kind of kernel call in one prompt step of ``tokens`` tokens and in one decode
+    step of ``batch`` requests at ``context`` tokens (eager launches, events around every call)."""
+    vocab = engine.spec.vocab_size
+    result = {}
+    prompt = _random_prompts(vocab, 1, tokens, 7)[0]
+    engine.step([("optime", prompt, [tokens - 1])])
+    engine.close("optime")
+    with _OpTimer(engine.ops) as t:
+        engine.step([("optime", prompt, [tokens - 1])])
+        result["prefill"] = t.table()
+    engine.close("optime")
+    rids = [f"opt{i}" for i in range(batch)]
+    prompts = _random_prompts(vocab, batch, context, 11)
+    prefill_all(engine, rids, prompts, engine.max_batch_tokens)
+    engine.step([(r, [1], [0]) for r in rids])
+    with _OpTimer(engine.ops) as t:
+        engine.step([(r, [2], [0]) for r in rids])
+        result["decode"] = t.table()
+    for r in rids:
+        engine.close(r)
+    return result
+
+
+def compare_designs(design: str = "sarizen", size: str = "small", steps: int = 64, warmup: int = 3, batch: int = 8,
+                    context: int = 2048, prefill_tokens: int = 2048, op_times: bool = True) -> int:
+    """Prefill and decode throughput of another design at layer sizes that resemble a real model's,
+    beside the Qwen3 dense decoder at the same width, depth, head count and active feed-forward
+    size (random bfloat16 weights); with ``op_times`` also the device time of every kind of kernel
+    call in one prompt step and one decode step of each.  Prints one JSON line."""
+    from .engine.engine import Engine
+    from .registry import config_from_dict
+    if design != "sarizen":
+        raise ValueError(f"unknown design '{design}'")
+    width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab = DESIGN_SIZES[size]
+    raw = _sarizen_shape(width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab)
+    dense = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=width,
+                 num_attention_heads=heads, num_key_value_heads=max(heads // 4, 1), head_dim=128,
+                 intermediate_size=top * expert_ff + shared_ff, vocab_size=vocab, rope_theta=1000000.0,
+                 rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False)
+    report = {"metric": f"prefill and decode tokens/s, {design} ({size}) beside the dense decoder at equal size",
+              "unit": "tokens/s", "dtype": "bf16", "n_gpus": 1,
+              "data": "synthetic: uniform random token ids, seeded random weights",
+              "config": {"width": width, "layers": layers, "heads": heads, "experts": experts, "top": top,
+                         "expert_ff": expert_ff, "shared_ff": shared_ff, "kv_rank": rank, "window": window,
+                         "vocab": vocab, "batch": batch, "context": context, "prefill_tokens": prefill_tokens},
+              "peaks": measured_peaks()}
+    for name, cfg in ((design, raw), ("qwen3", dense)):
+        config = config_from_dict(cfg)
+        engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=16,
+                                    max_tokens=batch * (context + 4 * steps + warmup + 192) + prefill_tokens,
+                                    max_requests=batch + 1, max_batch_tokens=max(prefill_tokens, 2048))
+        prefill_ms = time_prefill(engine, prefill_tokens, reps=3)
+        dec = time_decode(engine, batch, context, steps, warmup, reps=3)
+        entry = {"prefill_tokens_per_s": prefill_tokens / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+                 "decode_tokens_per_s": dec["tokens_per_s"], "decode_ms_per_step": dec["ms_per_step"],
+                 "decode_weight_bytes": engine.model.decode_weight_bytes()}
+        if op_times:
+            entry["op_ms"] = {phase: {k: round(v["ms"], 4) for k, v in sorted(tab.items(), key=lambda kv: -kv[1]["ms"])}
+                              for phase, tab in _op_times(engine, prefill_tokens, batch, context).items()}
+        report[name] = entry
+        del engine
+        torch.cuda.empty_cache()
+    report["value"] = report[design]["decode_tokens_per_s"]
+    print(json.dumps(report))
     return 0
