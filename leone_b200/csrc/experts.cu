@@ -1,6 +1,6 @@
 // Routed experts: router, grouping of (token, choice) pairs by expert, grouped products, combine.
 //
-//   z = W_router x (fp32),  s = sigmoid(z) or softmax(z),  the `top` largest s are chosen
+//   z = W_router x (an fp32 product of the framework's own),  s = sigmoid(z) or softmax(z),  the `top` largest s are chosen
 //   (lowest index first on equal scores); a pair's weight is its s, optionally divided by the sum
 //   of the chosen.  The weight multiplies the expert's input (`scale_input`) or its output.
 //   expert_e(a) = W_down_e (silu(W_gate_e a) * (W_up_e a))
@@ -16,35 +16,26 @@ namespace leone {
 
 __device__ __forceinline__ float silu_e(float z) { return z / (1.f + expf(-z)); }
 
-// One warp per token.
-template <typename T>
+// One warp per token: scores from the router's fp32 logits, then the `top` largest.
 __global__ void __launch_bounds__(128)
-route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, int n_tokens, int width, int experts,
-             int top, int softmax, int renormalize, int* __restrict__ chosen, float* __restrict__ weight) {
+select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int experts, int top, int softmax,
+              int renormalize, int* __restrict__ chosen, float* __restrict__ weight) {
   extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= n_tokens) return;
   float* sc = smem + (size_t)warp * experts;
-  const T* row = x + (size_t)t * ldx;
-  for (int e = 0; e < experts; ++e) {
-    const T* we = w + (size_t)e * width;
-    float dot = 0.f;
-    for (int c = lane; c < width; c += 32) dot = fmaf(to_float<T>(row[c]), to_float<T>(we[c]), dot);
-    dot = warp_sum(dot);
-    if (lane == 0) sc[e] = dot;
-  }
-  __syncwarp();
+  const float* row = logits + (size_t)t * ldl;
   if (softmax) {
     float m = -INFINITY;
-    for (int e = lane; e < experts; e += 32) m = fmaxf(m, sc[e]);
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, row[e]);
     m = warp_max(m);
     float sum = 0.f;
-    for (int e = lane; e < experts; e += 32) sum += expf(sc[e] - m);
+    for (int e = lane; e < experts; e += 32) sum += expf(row[e] - m);
     sum = warp_sum(sum);
-    for (int e = lane; e < experts; e += 32) sc[e] = expf(sc[e] - m) / sum;
+    for (int e = lane; e < experts; e += 32) sc[e] = expf(row[e] - m) / sum;
   } else {
-    for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+    for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-row[e]));
   }
   __syncwarp();
   float total = 0.f;
@@ -282,22 +273,13 @@ __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* 
 
 using namespace leone;
 
-extern "C" int leone_experts_route(int dtype, const void* x, int ldx, const void* w_router, int n_tokens,
-                                   int width, int experts, int top, int softmax, int renormalize, int* chosen,
-                                   float* weight, cudaStream_t stream) {
+// logits: fp32 [n_tokens, ldl] (the router's product); chosen, weight: [n_tokens * top].
+extern "C" int leone_experts_select(const float* logits, int ldl, int n_tokens, int experts, int top, int softmax,
+                                    int renormalize, int* chosen, float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048) return kRefusedSize;
-  const size_t smem = sizeof(float) * 4 * (size_t)experts;
-  const dim3 grid((n_tokens + 3) / 4);
-  if (dtype == 0)
-    route_kernel<float><<<grid, 128, smem, stream>>>((const float*)x, ldx, (const float*)w_router, n_tokens, width,
-                                                     experts, top, softmax, renormalize, chosen, weight);
-  else if (dtype == 1)
-    route_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, ldx,
-                                                             (const __nv_bfloat16*)w_router, n_tokens, width,
-                                                             experts, top, softmax, renormalize, chosen, weight);
-  else
-    return kRefusedDtype;
+  if (experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048 || ldl < experts) return kRefusedSize;
+  select_kernel<<<(n_tokens + 3) / 4, 128, sizeof(float) * 4 * (size_t)experts, stream>>>(
+      logits, ldl, n_tokens, experts, top, softmax, renormalize, chosen, weight);
   return launch_result();
 }
 

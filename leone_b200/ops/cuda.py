@@ -470,6 +470,14 @@ class CudaOps:
         if sink is not None:
             _need(sink.numel() == heads and sink.is_contiguous(), "attention_latent sink")
         self.launches += 1
+        if (q_abs.dtype == torch.bfloat16 and os.environ.get("LEONE_NO_LATENT_MMA", "0") != "1"
+                and self.mixers.leone_attention_latent_mma_supported(dk, dv)):
+            _check(self.mixers.leone_attention_latent_mma(
+                _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions),
+                n, heads, dk, dv, c_float(scale), int(window or 0), _ptr(sink), 0 if sink is None else _dt(sink.dtype),
+                _ptr(gate), 0 if gate is None else gate.stride(0), cache.page_tokens, kp.shape[0], bt.shape[0],
+                _ptr(ctx.status), self._stream()), "attention_latent_mma")
+            return
         _check(self.mixers.leone_attention_latent(
             _dt(q_abs.dtype), _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token),
             _ptr(ctx.positions), n, heads, dk, dv, c_float(scale), int(window or 0), _ptr(sink),
@@ -477,16 +485,20 @@ class CudaOps:
             cache.page_tokens, kp.shape[0], bt.shape[0], _ptr(ctx.status), self._stream()), "attention_latent")
 
     def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False):
-        """Router scores in fp32 and the ``top`` best experts of every token (``csrc/experts.cu``)."""
+        """Router logits as an fp32 product (bfloat16 operands multiply exactly in fp32), then the
+        scores and the ``top`` best experts of every token (``csrc/experts.cu``)."""
         n, width = x.shape
-        experts = w_router.shape[0]
-        _need(x.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == width and w_router.dtype == x.dtype
-              and chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top
+        if not isinstance(w_router, PreparedMatrix):
+            w_router = self.prepare_matrix(w_router)
+        experts = w_router.out_features
+        _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top
               and weight.numel() == n * top, "experts_route layout")
+        logits = self._scratch("router_logits", n, experts, torch.float32)
+        self.linear(x, w_router, logits)
         self.launches += 1
-        _check(self.mixers.leone_experts_route(_dt(x.dtype), _ptr(x), x.stride(0), _ptr(w_router), n, width, experts, top,
-                                               1 if softmax else 0, 1 if renormalize else 0, _ptr(chosen), _ptr(weight),
-                                               self._stream()), "experts_route")
+        _check(self.mixers.leone_experts_select(_ptr(logits), logits.stride(0), n, experts, top, 1 if softmax else 0,
+                                                1 if renormalize else 0, _ptr(chosen), _ptr(weight), self._stream()),
+               "experts_select")
 
     def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
         """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``."""

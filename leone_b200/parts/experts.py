@@ -61,7 +61,7 @@ class RoutedExperts(FeedForward):
         def stack(which):
             return torch.stack([tensors[self._expert(e, which)] for e in range(self.experts)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
-        self.w_router = tensors[self.router_name].contiguous()
+        self.w_router = self.rt.ops.prepare_matrix(tensors[self.router_name].contiguous())
         if self.shared_ff:
             ops = self.rt.ops
             self.w_shared_gate_up = ops.prepare_gate_up(tensors[self.shared_pattern.format("gate")],
