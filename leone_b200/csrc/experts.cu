@@ -269,6 +269,195 @@ __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* 
   }
 }
 
+
+// ---- the grouped products on tensor cores (bfloat16) ----------------------------------------------
+// A row tile of 64 sorted pairs of one expert times 64 output columns; four warps of 16 rows each;
+// operands come through a three-stage cp.async ring in shared memory (rows of 32 k-values, padded
+// so that ldmatrix finds eight rows in eight different banks).  NB = 2: gate and up together, with
+// the activation in the epilogue; NB = 1: the down product.  Because the products are linear, the
+// pair's weight multiplies the fp32 sums in the epilogue instead of the gathered input rows.
+constexpr int TM = 64, TN = 64, TK = 32, TSTAGES = 3, TPITCH = TK * 2 + 16;
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// a_rows: row r of the tile reads a_base + a_index[r] * lda (a_index < 0: a row of zeros).
+template <int NB>
+__device__ __forceinline__ void grouped_mainloop(unsigned char* smem, const __nv_bfloat16* a_base, const int* a_index_s,
+                                                 int lda, const __nv_bfloat16* b0_base, const __nv_bfloat16* b1_base,
+                                                 int n_valid, int K, float (*acc)[8][4]) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kStageBytes = (TM + NB * TN) * TPITCH;
+  const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem);
+  const int kblocks = (K + TK - 1) / TK;
+  auto load = [&](int kb, int stage) {
+    const uint32_t st = base + stage * kStageBytes;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + i * 128, row = c >> 2, kc = c & 3;
+      const int k = kb * TK + kc * 8;
+      const int ai = a_index_s[row];
+      const bool av = ai >= 0 && k < K;
+      cp_async16_zfill(st + row * TPITCH + kc * 16, av ? (const void*)(a_base + (size_t)ai * lda + k) : (const void*)a_base, av);
+      const bool bv = row < n_valid && k < K;
+      cp_async16_zfill(st + (TM + row) * TPITCH + kc * 16, bv ? (const void*)(b0_base + (size_t)row * K + k) : (const void*)b0_base, bv);
+      if (NB == 2)
+        cp_async16_zfill(st + (TM + TN + row) * TPITCH + kc * 16,
+                         bv ? (const void*)(b1_base + (size_t)row * K + k) : (const void*)b1_base, bv);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  for (int s = 0; s < TSTAGES - 1; ++s) {
+    if (s < kblocks) load(s, s);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  const int mi = lane >> 3;
+  for (int kb = 0; kb < kblocks; ++kb) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(TSTAGES - 2) : "memory");
+    __syncthreads();
+    if (kb + TSTAGES - 1 < kblocks) load(kb + TSTAGES - 1, (kb + TSTAGES - 1) % TSTAGES);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t st = base + (kb % TSTAGES) * kStageBytes;
+#pragma unroll
+    for (int ks = 0; ks < TK / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm4(st + (warp * 16 + (lane & 15)) * TPITCH + (lane >> 4) * 16 + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+      for (int m = 0; m < NB; ++m) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          uint32_t b0, b1, b2, b3;
+          ldsm4(st + (TM + m * TN + np * 16 + (lane & 7) + (mi >> 1) * 8) * TPITCH + (mi & 1) * 16 + ks * 32, b0, b1, b2, b3);
+          mma16816(acc[m][2 * np], a0, a1, a2, a3, b0, b1);
+          mma16816(acc[m][2 * np + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+__device__ __forceinline__ bool find_tile_m(const int* __restrict__ offsets, int experts, int tile, int& expert,
+                                            int& row0, int& row1) {
+  int before = 0;
+  for (int e = 0; e < experts; ++e) {
+    const int b = offsets[e], n = offsets[e + 1] - b;
+    const int tiles = (n + TM - 1) / TM;
+    if (tile < before + tiles) {
+      expert = e;
+      row0 = b + (tile - before) * TM;
+      row1 = min(row0 + TM, b + n);
+      return true;
+    }
+    before += tiles;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(128)
+experts_gate_up_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w_gate,
+                           const __nv_bfloat16* __restrict__ w_up, __nv_bfloat16* __restrict__ act,
+                           const int* __restrict__ offsets, const int* __restrict__ order,
+                           const float* __restrict__ weight, int experts, int top, int width, int ff,
+                           int scale_input) {
+  extern __shared__ __align__(16) unsigned char smem_m[];
+  __shared__ int a_index[TM];
+  __shared__ float a_weight[TM];
+  int expert, row0, row1;
+  if (!find_tile_m(offsets, experts, blockIdx.y, expert, row0, row1)) return;
+  const int n0 = blockIdx.x * TN;
+  for (int r = threadIdx.x; r < TM; r += 128) {
+    const bool ok = row0 + r < row1;
+    const int pair = ok ? order[row0 + r] : 0;
+    a_index[r] = ok ? pair / top : -1;
+    a_weight[r] = (ok && scale_input) ? weight[pair] : 1.f;
+  }
+  __syncthreads();
+  float acc[2][8][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+  grouped_mainloop<2>(smem_m, x, a_index, ldx, w_gate + ((size_t)expert * ff + n0) * width,
+                      w_up + ((size_t)expert * ff + n0) * width, min(TN, ff - n0), width, acc);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g + 8 * i;
+    if (row0 + r >= row1) continue;
+    const float w = a_weight[r];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int col = n0 + n * 8 + 2 * tq;
+      if (col >= ff) continue;
+      float v[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float gg = round_to<__nv_bfloat16>(acc[0][n][2 * i + j] * w);
+        const float uu = round_to<__nv_bfloat16>(acc[1][n][2 * i + j] * w);
+        v[j] = silu_e(gg) * uu;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(act + (size_t)(row0 + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+experts_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down,
+                        float* __restrict__ pair_out, const int* __restrict__ offsets,
+                        const int* __restrict__ order, const float* __restrict__ weight, int experts, int width,
+                        int ff, int scale_input) {
+  extern __shared__ __align__(16) unsigned char smem_m[];
+  __shared__ int a_index[TM];
+  __shared__ int a_pair[TM];
+  int expert, row0, row1;
+  if (!find_tile_m(offsets, experts, blockIdx.y, expert, row0, row1)) return;
+  const int n0 = blockIdx.x * TN;
+  for (int r = threadIdx.x; r < TM; r += 128) {
+    const bool ok = row0 + r < row1;
+    a_index[r] = ok ? row0 + r : -1;
+    a_pair[r] = ok ? order[row0 + r] : 0;
+  }
+  __syncthreads();
+  float acc[1][8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[0][n][i] = 0.f;
+  grouped_mainloop<1>(smem_m, act, a_index, ff, w_down + ((size_t)expert * width + n0) * ff, nullptr,
+                      min(TN, width - n0), ff, acc);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g + 8 * i;
+    if (row0 + r >= row1) continue;
+    const int pair = a_pair[r];
+    const float f = scale_input ? 1.f : weight[pair];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int col = n0 + n * 8 + 2 * tq;
+      if (col >= width) continue;
+      *reinterpret_cast<float2*>(pair_out + (size_t)pair * width + col) =
+          make_float2(acc[0][n][2 * i] * f, acc[0][n][2 * i + 1] * f);
+    }
+  }
+}
+
 }  // namespace leone
 
 using namespace leone;
@@ -288,13 +477,35 @@ extern "C" int leone_experts_select(const float* logits, int ldl, int n_tokens, 
 extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const void* w_gate, const void* w_up,
                                      const void* w_down, const int* chosen, const float* weight, int n_tokens,
                                      int width, int ff, int experts, int top, int scale_input, int* offsets,
-                                     int* order, void* act, float* pair_out, float* hidden,
+                                     int* order, void* act, float* pair_out, float* hidden, int tensor_cores,
                                      cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (width <= 0 || ff <= 0 || experts <= 0 || top <= 0 || experts > 8192) return kRefusedSize;
   const long long pairs = (long long)n_tokens * top;
   if (pairs > (1 << 30)) return kRefusedSize;
   group_pairs_kernel<<<1, 1024, sizeof(int) * (size_t)experts, stream>>>(chosen, (int)pairs, experts, offsets, order);
+  if (tensor_cores && dtype == 1 && width % 8 == 0 && ff % 8 == 0 && ldx % 8 == 0) {
+    const long long tiles = (pairs + TM - 1) / TM + (experts < pairs ? experts : pairs);
+    if (tiles > 65535) return kRefusedSize;
+    const size_t smem_up = (size_t)TSTAGES * (TM + 2 * TN) * TPITCH, smem_down = (size_t)TSTAGES * (TM + TN) * TPITCH;
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(experts_gate_up_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+      cudaFuncSetAttribute(experts_down_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+      configured = true;
+    }
+    experts_gate_up_mma_kernel<<<dim3((ff + TN - 1) / TN, (unsigned)tiles), 128, smem_up, stream>>>(
+        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, (__nv_bfloat16*)act,
+        offsets, order, weight, experts, top, width, ff, scale_input);
+    experts_down_mma_kernel<<<dim3((width + TN - 1) / TN, (unsigned)tiles), 128, smem_down, stream>>>(
+        (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, pair_out, offsets, order, weight, experts, width, ff,
+        scale_input);
+    const long long total = (long long)n_tokens * width;
+    const long long blocks = (total + 255) / 256;
+    experts_combine_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(hidden, pair_out,
+                                                                                                total, width, top);
+    return launch_result();
+  }
   // every expert may end with a partly filled tile
   const long long max_tiles = (pairs + GM - 1) / GM + (experts < pairs ? experts : pairs);
   if (max_tiles > 65535) return kRefusedSize;

@@ -518,7 +518,8 @@ class CudaOps:
         _check(self.mixers.leone_experts_forward(
             _dt(x.dtype), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(chosen), _ptr(weight), n,
             width, ff, experts, top, 1 if scale_input else 0, _ptr(offsets), _ptr(order), _ptr(act), _ptr(pair_out),
-            _ptr(hidden), self._stream()), "experts_forward")
+            _ptr(hidden), 0 if os.environ.get("LEONE_NO_EXPERT_MMA", "0") == "1" else 1, self._stream()),
+            "experts_forward")
 
     def sample(self, logits, temperature, seeds, positions, out):
         rows, vocab = logits.shape
