@@ -7,7 +7,9 @@
 // elements) for O += P V.  Warp w computes the scores of keys 16w..16w+15 of the tile; the rows'
 // maxima and sums cross the warps through shared memory (fp32 online softmax, the per-head sink as
 // the first score); P goes to shared memory as bfloat16 and every warp multiplies it with its
-// quarter of the value columns.  O stays in registers (16 x dv/4 fp32 per warp).
+// quarter of the value columns.  O stays in registers (16 x dv/4 fp32 per warp).  A step of few tokens
+// (decode) splits each token's keys over several blocks, which leave (O, m, l) in scratch for a merge
+// kernel that also adds the sink and applies the gate.
 //
 // Sizes: dk a multiple of 16, dv = 32 * NT with NT in {2, 4, 6, 8, 12, 16}; other sizes take the
 // any-size kernel of attention_latent.cu.
@@ -51,7 +53,8 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
                             int table_width, const int* __restrict__ seq_of_token,
                             const int* __restrict__ positions, int heads, int dk, float scale, int window,
                             const TS* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
-                            int page_tokens, int num_pages, int n_seqs, int* status) {
+                            int page_tokens, int num_pages, int n_seqs, int splits, float* __restrict__ partial,
+                            int* status) {
   constexpr int dv = 32 * NT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = dk * 2 + 16;                       // bytes per row of K and Q: no two of 8 rows share a bank
@@ -68,10 +71,17 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
   const int pos = positions[t], s = seq_of_token[t];
   const int nh = min(16, heads - h0);
   if (tid == 0) bad = 0;
+  // with several splits, this block's rows of the partial results: [16][dv + 2] floats (O, m, l)
+  float* mine = splits > 1 ? partial + (((size_t)t * gridDim.y + blockIdx.y) * splits + blockIdx.z) * 16 * (dv + 2)
+                           : nullptr;
   if (s < 0 || s >= n_seqs || pos < 0) {
     if (tid == 0) set_status(status, s < 0 || s >= n_seqs ? kBadSequence : kBadPosition, t, pos);
-    for (int i = tid; i < nh * dv; i += kMmaThreads)
-      out[((size_t)t * heads + h0) * dv + i] = __float2bfloat16_rn(0.f);
+    if (mine != nullptr) {
+      for (int i = tid; i < 16 * (dv + 2); i += kMmaThreads) mine[i] = (i % (dv + 2)) == dv ? -INFINITY : 0.f;
+    } else {
+      for (int i = tid; i < nh * dv; i += kMmaThreads)
+        out[((size_t)t * heads + h0) * dv + i] = __float2bfloat16_rn(0.f);
+    }
     return;
   }
   const uint32_t k_base = (uint32_t)__cvta_generic_to_shared(k_s);
@@ -88,7 +98,7 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   // running maximum and denominator of the thread's two rows (g and g + 8); the sink is a score
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  if (sink != nullptr) {
+  if (sink != nullptr && splits == 1) {            // with several splits the merge adds the sink
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int r = g + 8 * i;
@@ -104,7 +114,15 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
 
-  for (int j0 = lo; j0 <= pos; j0 += kTile) {
+  // this block's share of the token's key tiles
+  int j_first = lo, j_last = pos;
+  if (splits > 1) {
+    const int tiles = (pos - lo) / kTile + 1;
+    const int per = (tiles + splits - 1) / splits;
+    j_first = lo + (int)blockIdx.z * per * kTile;
+    j_last = min(pos, j_first + per * kTile - 1);
+  }
+  for (int j0 = j_first; j0 <= j_last; j0 += kTile) {
     __syncthreads();                                   // the tile before is no longer read
     // copy the tile's rows from their pages (rows past the query's position are zero)
     for (int r = warp; r < kTile; r += 4) {
@@ -236,6 +254,20 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
   }
   __syncthreads();
   const int failed = bad;
+  if (mine != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float* row = mine + (g + 8 * i) * (dv + 2);
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        *reinterpret_cast<float2*>(row + warp * (dv / 4) + n * 8 + 2 * tq) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+      if (warp == 0 && tq == 0) {
+        row[dv] = m_run[i];
+        row[dv + 1] = failed ? NAN : l_run[i];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = g + 8 * i;
@@ -246,6 +278,36 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
 #pragma unroll
     for (int n = 0; n < NT; ++n)
       *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * tq) = pack_bf16(o[n][2 * i] * f, o[n][2 * i + 1] * f);
+  }
+}
+
+// The splits of a (token, head): out = sum_z O_z e^(m_z - m) / (sum_z l_z e^(m_z - m) + e^(sink - m)),
+// times sigmoid(gate).  One block per (token, head).
+template <typename TS>
+__global__ void __launch_bounds__(128)
+attention_latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int heads, int dv,
+                              int splits, const TS* __restrict__ sink, const __nv_bfloat16* __restrict__ gate,
+                              int ldg) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int groups = (heads + 15) / 16;
+  const float* base = partial + (((size_t)t * groups + h / 16) * splits) * 16 * (dv + 2) + (size_t)(h % 16) * (dv + 2);
+  const size_t step = (size_t)16 * (dv + 2);
+  float m = sink != nullptr ? to_float<TS>(sink[h]) : -INFINITY;
+  for (int z = 0; z < splits; ++z) m = fmaxf(m, base[z * step + dv]);
+  float l = sink != nullptr ? expf(to_float<TS>(sink[h]) - m) : 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float mz = base[z * step + dv];
+    if (mz != -INFINITY) l += base[z * step + dv + 1] * expf(mz - m);
+  }
+  float f = l > 0.f ? 1.f / l : 0.f;          // a NaN denominator (a bad page in some split) gives zeros
+  if (gate != nullptr) f *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + h])));
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = base[z * step + dv];
+      if (mz != -INFINITY) acc += base[z * step + c] * expf(mz - m);
+    }
+    out[((size_t)t * heads + h) * dv + c] = __float2bfloat16_rn(acc * f);
   }
 }
 
@@ -264,12 +326,13 @@ extern "C" int leone_attention_latent_mma(const void* q, void* out, const void* 
                                           int table_width, const int* seq_of_token, const int* positions,
                                           int n_tokens, int heads, int dk, int dv, float scale, int window,
                                           const void* sink, int sink_dtype, const void* gate, int ldg,
-                                          int page_tokens, int num_pages, int n_seqs, int* status,
-                                          cudaStream_t stream) {
+                                          int page_tokens, int num_pages, int n_seqs, int splits, float* partial,
+                                          int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (!leone_attention_latent_mma_supported(dk, dv) || heads <= 0 || page_tokens <= 0 || table_width <= 0)
+  if (!leone_attention_latent_mma_supported(dk, dv) || heads <= 0 || page_tokens <= 0 || table_width <= 0 ||
+      splits < 1 || splits > 64 || (splits > 1 && partial == nullptr))
     return kRefusedSize;
-  const dim3 grid(n_tokens, (heads + 15) / 16);
+  const dim3 grid(n_tokens, (heads + 15) / 16, splits);
   if (grid.y > 65535) return kRefusedSize;
   const int pitch = dk * 2 + 16;
   const size_t smem = (size_t)(kTile + 16) * pitch + 16 * (kTile * 2 + 16) + 128 * sizeof(float);
@@ -281,7 +344,7 @@ extern "C" int leone_attention_latent_mma(const void* q, void* out, const void* 
                                               (const __nv_bfloat16*)pool, block_table, table_width,          \
                                               seq_of_token, positions, heads, dk, scale, window,             \
                                               (const TS*)sink, (const __nv_bfloat16*)gate, ldg, page_tokens,  \
-                                              num_pages, n_seqs, status);                                     \
+                                              num_pages, n_seqs, splits, partial, status);                    \
   } while (0)
 #define BY_NT(TS)                       \
   switch (dv / 32) {                    \
@@ -297,5 +360,14 @@ extern "C" int leone_attention_latent_mma(const void* q, void* out, const void* 
   else return kRefusedDtype;
 #undef BY_NT
 #undef LAUNCH
+  if (splits > 1) {
+    const dim3 mgrid(n_tokens, heads);
+    if (sink_dtype == 0)
+      attention_latent_merge_kernel<float><<<mgrid, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, heads, dv, splits,
+                                                                      (const float*)sink, (const __nv_bfloat16*)gate, ldg);
+    else
+      attention_latent_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(
+          partial, (__nv_bfloat16*)out, heads, dv, splits, (const __nv_bfloat16*)sink, (const __nv_bfloat16*)gate, ldg);
+  }
   return launch_result();
 }

@@ -10,8 +10,8 @@
 //
 // Two forms:
 //  * `scan`: one block per (value slice, head, sequence) walks the step's tokens of its sequence
-//    in order.  The block's threads are (32 value columns) x (DP parts of the key dimension);
-//    a thread keeps its part of a state column in registers.
+//    in order.  The block's threads are (32 lanes of value columns) x (DP parts of the key
+//    dimension); a thread keeps its rows of one or four state columns in registers.
 //  * chunk-parallel (long prompt portions): a sequence's tokens are cut into chunks of `chunk`
 //    tokens; (1) every chunk but the last sums its own k v^T contributions from a zero state,
 //    (2) a pass over the chunks turns those into the state at each chunk's start
@@ -31,9 +31,11 @@ constexpr int kTB = 8;         // tokens staged in shared memory at a time
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
-// mode 0: state from `state_in` (or zero if null), outputs written, final state to `state_out` (if not null)
-// mode 1: state from zero, no outputs, final state to `state_out` (a chunk's own contribution)
-template <typename T, int DPT>
+// mode 0: state from `chunk_state`/the slot, outputs written, final state to the slot (last chunk)
+// mode 1: state from zero, no outputs, final state to `chunk_state` (a chunk's own contribution)
+// A thread owns VPT value columns of DPT rows of the state, so a k or q element read from shared
+// memory serves VPT multiply-adds.
+template <typename T, int DPT, int VPT>
 __global__ void __launch_bounds__(256)
 linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                              float* __restrict__ out, int ldo, float* state, float* chunk_state,
@@ -41,17 +43,17 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int 
                              const float* __restrict__ decay, int heads, int dim, int vdim,
                              int chunk, int mode, int n_seqs, int n_slots, int* status) {
   extern __shared__ __align__(16) float smem[];
+  constexpr int VW = kVS * VPT;            // value columns per block
   const int DP = blockDim.y;
   float* q_s = smem;                       // [kTB][dim]
   float* k_s = q_s + kTB * dim;            // [kTB][dim]
-  float* v_s = k_s + kTB * dim;            // [kTB][kVS]
-  float* part = v_s + kTB * kVS;           // [DP][kTB][kVS]
+  float* v_s = k_s + kTB * dim;            // [kTB][VW]
+  float* part = v_s + kTB * VW;            // [DP][kTB][VW]
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int tid = ty * kVS + tx, nthreads = kVS * DP;
   const int h = blockIdx.y;
   int s = blockIdx.z, c = 0;
-  const int v0 = blockIdx.x * kVS;
-  const int v = v0 + tx;
+  const int v0 = blockIdx.x * VW;
   int t0, t1;
   if (chunk > 0) {
     // blockIdx.z counts (sequence, chunk) pairs: find this block's
@@ -99,11 +101,15 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int 
     s_in = slot_state;
     s_out = slot_state;
   }
-  float S[DPT];
+  float S[DPT][VPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
     const int d = d0 + i;
-    S[i] = (s_in != nullptr && i < d_per && d < dim && v < vdim) ? s_in[(size_t)d * vdim + v] : 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = v0 + j * kVS + tx;
+      S[i][j] = (s_in != nullptr && i < d_per && d < dim && v < vdim) ? s_in[(size_t)d * vdim + v] : 0.f;
+    }
   }
   for (int tb = t0; tb < t1; tb += kTB) {
     const int nt = min(kTB, t1 - tb);
@@ -114,44 +120,57 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int 
       q_s[tt * dim + d] = silu_f(to_float<T>(row[q_off]));
       k_s[tt * dim + d] = silu_f(to_float<T>(row[k_off]));
     }
-    for (int i = tid; i < nt * kVS; i += nthreads) {
-      const int tt = i / kVS, vv = i - tt * kVS;
+    for (int i = tid; i < nt * VW; i += nthreads) {
+      const int tt = i / VW, vv = i - tt * VW;
       v_s[i] = v0 + vv < vdim
                    ? silu_f(to_float<T>(proj[(size_t)(tb + tt) * ld + v_off + (size_t)h * vdim + v0 + vv]))
                    : 0.f;
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float vt = v_s[tt * kVS + tx];
+      float vt[VPT], acc[VPT];
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        vt[j] = v_s[tt * VW + j * kVS + tx];
+        acc[j] = 0.f;
+      }
       const float* kk = k_s + tt * dim + d0;
       const float* qq = q_s + tt * dim + d0;
-      float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         if (i < d_per && d0 + i < dim) {
-          S[i] = fmaf(dec, S[i], kk[i] * vt);
-          acc = fmaf(S[i], qq[i], acc);
+          const float kv = kk[i], qv = qq[i];
+#pragma unroll
+          for (int j = 0; j < VPT; ++j) {
+            S[i][j] = fmaf(dec, S[i][j], kv * vt[j]);
+            acc[j] = fmaf(S[i][j], qv, acc[j]);
+          }
         }
       }
-      part[(ty * kTB + tt) * kVS + tx] = acc;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) part[(ty * kTB + tt) * VW + j * kVS + tx] = acc[j];
     }
     if (mode == 0) {
       __syncthreads();
-      for (int i = tid; i < nt * kVS; i += nthreads) {
-        const int tt = i / kVS, vv = i - tt * kVS;
+      for (int i = tid; i < nt * VW; i += nthreads) {
+        const int tt = i / VW, vv = i - tt * VW;
         if (v0 + vv < vdim) {
           float sum = 0.f;
-          for (int p = 0; p < DP; ++p) sum += part[(p * kTB + tt) * kVS + vv];
+          for (int p = 0; p < DP; ++p) sum += part[(p * kTB + tt) * VW + vv];
           out[(size_t)(tb + tt) * ldo + (size_t)h * vdim + v0 + vv] = sum;
         }
       }
     }
   }
-  if (s_out != nullptr && v < vdim) {
+  if (s_out != nullptr) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
       const int d = d0 + i;
-      if (i < d_per && d < dim) s_out[(size_t)d * vdim + v] = S[i];
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int v = v0 + j * kVS + tx;
+        if (i < d_per && d < dim && v < vdim) s_out[(size_t)d * vdim + v] = S[i][j];
+      }
     }
   }
 }
@@ -223,23 +242,32 @@ extern "C" int leone_linear_attention(int dtype, const void* proj, int ld, int q
   if (n_seqs <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || n_seqs > 65535 || dim > 512) return kRefusedSize;
   if (chunk < 0 || (chunk > 0 && (n_chunks <= 0 || n_chunks > 65535 || chunk_state == nullptr))) return kRefusedSize;
-  int dp = 4, dpt;
-  if (dim > 256) dp = 8;
+  // DP parts of the key dimension of at most 16 rows each (up to 8 parts), 1 or 4 value columns a thread
+  int dp = (dim + 15) / 16;
+  if (dp > 8) dp = 8;
   const int d_per = (dim + dp - 1) / dp;
-  dpt = d_per <= 8 ? 8 : d_per <= 16 ? 16 : d_per <= 32 ? 32 : 64;
+  const int dpt = d_per <= 8 ? 8 : d_per <= 16 ? 16 : d_per <= 32 ? 32 : 64;
+  const int vpt = (vdim > 32 && dpt <= 32) ? 4 : 1;
   const dim3 block(kVS, dp);
-  const size_t smem = sizeof(float) * ((size_t)2 * kTB * dim + kTB * kVS + (size_t)dp * kTB * kVS);
-  const int vslices = (vdim + kVS - 1) / kVS;
-#define SCAN(T, D, GRIDZ, MODE)                                                                            \
-  linear_attention_scan_kernel<T, D><<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(                  \
+  const int vw = kVS * vpt;
+  const size_t smem = sizeof(float) * ((size_t)2 * kTB * dim + kTB * vw + (size_t)dp * kTB * vw);
+  const int vslices = (vdim + vw - 1) / vw;
+#define SCAN(T, D, V, GRIDZ, MODE)                                                                         \
+  linear_attention_scan_kernel<T, D, V><<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(               \
       (const T*)proj, ld, q_off, k_off, v_off, out, ldo, state, chunk_state, q_start, slot_ids, decay,     \
       heads, dim, vdim, chunk, MODE, n_seqs, n_slots, status)
-#define SCAN_D(T, GRIDZ, MODE)                          \
-  do {                                                  \
-    if (dpt == 8) SCAN(T, 8, GRIDZ, MODE);              \
-    else if (dpt == 16) SCAN(T, 16, GRIDZ, MODE);       \
-    else if (dpt == 32) SCAN(T, 32, GRIDZ, MODE);       \
-    else SCAN(T, 64, GRIDZ, MODE);                      \
+#define SCAN_D(T, GRIDZ, MODE)                                      \
+  do {                                                              \
+    if (vpt == 4) {                                                 \
+      if (dpt == 8) SCAN(T, 8, 4, GRIDZ, MODE);                     \
+      else if (dpt == 16) SCAN(T, 16, 4, GRIDZ, MODE);              \
+      else SCAN(T, 32, 4, GRIDZ, MODE);                             \
+    } else {                                                        \
+      if (dpt == 8) SCAN(T, 8, 1, GRIDZ, MODE);                     \
+      else if (dpt == 16) SCAN(T, 16, 1, GRIDZ, MODE);              \
+      else if (dpt == 32) SCAN(T, 32, 1, GRIDZ, MODE);              \
+      else SCAN(T, 64, 1, GRIDZ, MODE);                             \
+    }                                                               \
   } while (0)
 #define SCAN_T(GRIDZ, MODE)                             \
   do {                                                  \

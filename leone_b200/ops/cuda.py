@@ -472,11 +472,19 @@ class CudaOps:
         self.launches += 1
         if (q_abs.dtype == torch.bfloat16 and os.environ.get("LEONE_NO_LATENT_MMA", "0") != "1"
                 and self.mixers.leone_attention_latent_mma_supported(dk, dv)):
+            # few tokens (decode): a token's keys are split over blocks until the SMs are busy
+            groups = -(-heads // 16)
+            keys = min(int(window), ctx.max_ctx_len) if window else ctx.max_ctx_len
+            splits = max(1, min(16, -(-keys // 64), 148 // max(n * groups, 1)))
+            partial = None
+            if splits > 1:
+                partial = self._scratch("latent_partial", n * groups * splits * 16, dv + 2, torch.float32)
+                self.launches += 1
             _check(self.mixers.leone_attention_latent_mma(
                 _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions),
                 n, heads, dk, dv, c_float(scale), int(window or 0), _ptr(sink), 0 if sink is None else _dt(sink.dtype),
                 _ptr(gate), 0 if gate is None else gate.stride(0), cache.page_tokens, kp.shape[0], bt.shape[0],
-                _ptr(ctx.status), self._stream()), "attention_latent_mma")
+                splits, _ptr(partial), _ptr(ctx.status), self._stream()), "attention_latent_mma")
             return
         _check(self.mixers.leone_attention_latent(
             _dt(q_abs.dtype), _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token),
