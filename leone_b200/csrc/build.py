@@ -41,7 +41,7 @@ MODULES: Dict[str, List[str]] = {
     "host": ["host_runtime.cpp", "random_weights_host.cpp"],
 }
 HOST_ONLY = {"host"}
-HEADERS = ["common.cuh", "tc_common.cuh", "gemm_parts.cuh", "leone_static.h", "attention_tiled.cu", "random_draw.h"]
+HEADERS = ["common.cuh", "mma_tile.cuh", "tc_common.cuh", "gemm_parts.cuh", "leone_static.h", "attention_tiled.cu", "random_draw.h"]
 
 # -fno-gnu-unique: statics inside inline functions and templates (the once-per-kernel set-up
 # flags, the launch mode switch) must belong to one library image each; with GNU unique

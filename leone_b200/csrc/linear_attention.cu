@@ -26,7 +26,7 @@
 namespace leone {
 
 constexpr int kVS = 32;        // value columns per block
-constexpr int kTB = 8;         // tokens staged in shared memory at a time
+constexpr int kTB = 16;        // tokens staged in shared memory at a time
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
@@ -252,10 +252,15 @@ extern "C" int leone_linear_attention(int dtype, const void* proj, int ld, int q
   const int vw = kVS * vpt;
   const size_t smem = sizeof(float) * ((size_t)2 * kTB * dim + kTB * vw + (size_t)dp * kTB * vw);
   const int vslices = (vdim + vw - 1) / vw;
+  if (smem > 200 * 1024) return kRefusedSize;
 #define SCAN(T, D, V, GRIDZ, MODE)                                                                         \
-  linear_attention_scan_kernel<T, D, V><<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(               \
-      (const T*)proj, ld, q_off, k_off, v_off, out, ldo, state, chunk_state, q_start, slot_ids, decay,     \
-      heads, dim, vdim, chunk, MODE, n_seqs, n_slots, status)
+  do {                                                                                                     \
+    auto kern = linear_attention_scan_kernel<T, D, V>;                                                     \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    kern<<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(                                            \
+        (const T*)proj, ld, q_off, k_off, v_off, out, ldo, state, chunk_state, q_start, slot_ids, decay,   \
+        heads, dim, vdim, chunk, MODE, n_seqs, n_slots, status);                                           \
+  } while (0)
 #define SCAN_D(T, GRIDZ, MODE)                                      \
   do {                                                              \
     if (vpt == 4) {                                                 \

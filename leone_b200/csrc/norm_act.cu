@@ -1,6 +1,7 @@
 // Small kernels shared by several parts: two RMS norms of the same rows in one pass, the squared
 // ReLU, and a product batched over heads.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 namespace leone {
 
@@ -90,6 +91,40 @@ gemm_batched_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __restr
   }
 }
 
+// The same product on tensor cores (bfloat16): a block owns 64 rows x 64 columns of one batch.
+__global__ void __launch_bounds__(128)
+gemm_batched_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                        __nv_bfloat16* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc, long long a_bs,
+                        long long w_bs, long long c_bs) {
+  extern __shared__ __align__(16) unsigned char smem_m[];
+  __shared__ int a_index[TM];
+  A += (size_t)blockIdx.z * a_bs;
+  W += (size_t)blockIdx.z * w_bs;
+  C += (size_t)blockIdx.z * c_bs;
+  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  for (int r = threadIdx.x; r < TM; r += 128) a_index[r] = m0 + r < M ? m0 + r : -1;
+  __syncthreads();
+  float acc[1][8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[0][n][i] = 0.f;
+  grouped_mainloop<1>(smem_m, A, a_index, lda, W + (size_t)n0 * ldw, nullptr, min(TN, N - n0), K, acc, ldw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + warp * 16 + g + 8 * i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int col = n0 + n * 8 + 2 * tq;
+      if (col >= N) continue;
+      *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + col) =
+          __floats2bfloat162_rn(acc[0][n][2 * i], acc[0][n][2 * i + 1]);
+    }
+  }
+}
+
 }  // namespace leone
 
 using namespace leone;
@@ -127,6 +162,21 @@ extern "C" int leone_gemm_batched(int dtype, const void* a, const void* w, void*
   if (k <= 0 || lda < k || ldw < k || ldc < n || batch > 65535) return kRefusedSize;
   const dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM, batch);
   if (grid.y > 65535) return kRefusedSize;
+  // bfloat16 with 16-byte aligned rows: tensor cores
+  if (dtype == 1 && k % 8 == 0 && n % 2 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldc % 2 == 0 && a_bs % 8 == 0 &&
+      w_bs % 8 == 0 && c_bs % 2 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)c % 4) == 0) {
+    const dim3 tgrid((n + TN - 1) / TN, (m + TM - 1) / TM, batch);
+    if (tgrid.y > 65535) return kRefusedSize;
+    const size_t smem = (size_t)TSTAGES * (TM + TN) * TPITCH;
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(gemm_batched_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      configured = true;
+    }
+    gemm_batched_mma_kernel<<<tgrid, 128, smem, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+                                                          (__nv_bfloat16*)c, m, n, k, lda, ldw, ldc, a_bs, w_bs, c_bs);
+    return launch_result();
+  }
   if (dtype == 0)
     gemm_batched_kernel<float><<<grid, 256, 0, stream>>>((const float*)a, (const float*)w, (float*)c, m, n, k, lda,
                                                          ldw, ldc, a_bs, w_bs, c_bs);

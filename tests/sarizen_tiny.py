@@ -54,8 +54,15 @@ TINY = {
                                                      scaling={"factor": 8.0, "original": 128, "fast": 32.0, "slow": 1.0}),
          "mlp": moe(64, 8, 2, 64)},
         {"type": "lightning", "mixer": lightning(4, 64, 64, [0.6, 0.9, 0.99, 0.999]), "mlp": {"kind": "dense", "ff": 256}}]},
+    # 18 heads (two groups of query rows on the tensor-core attention), no window on one latent layer,
+    # value width 128, keys of 80 and 144 elements, a wide lightning head
+    "S": {"architecture": "Sarizen", "vocab": 200, "width": 96, "norm": {"eps": 1e-6}, "logit_scale": 0.25, "layers": [
+        {"type": "latent_attention", "mixer": latent(18, 16, 16, 8, 64, 0.2, base=1000.0, dims=8), "mlp": None},
+        {"type": "lightning", "mixer": lightning(2, 136, 40, [0.8, 0.99]), "mlp": moe(24, 6, 6, 16)},
+        {"type": "latent_attention", "mixer": latent(5, 32, 16, 32, 128, 0.12, window=70, scaling=YARN),
+         "mlp": {"kind": "dense", "ff": 64}}]},
 }
-PAGE_TOKENS = {"P": 4, "Q": 8, "R": 16}
+PAGE_TOKENS = {"P": 4, "Q": 8, "R": 16, "S": 32}
 
 
 def tiny_config(which):

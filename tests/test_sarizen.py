@@ -106,7 +106,7 @@ def test_cache_requests_of_the_mixers():
 
 # -- on the GPU ----------------------------------------------------------------------------------
 @pytest.mark.gpu
-@pytest.mark.parametrize("which", ["P", "Q", "R"])
+@pytest.mark.parametrize("which", ["P", "Q", "R", "S"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_replay_on_the_gpu(which, dtype, mode):
