@@ -35,13 +35,14 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 // mode 1: state from zero, no outputs, final state to `chunk_state` (a chunk's own contribution)
 // A thread owns VPT value columns of DPT rows of the state, so a k or q element read from shared
 // memory serves VPT multiply-adds.
-template <typename T, int DPT, int VPT>
+template <typename T, int DPT, int VPT, bool OUT, bool FAST>
 __global__ void __launch_bounds__(256)
 linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                              float* __restrict__ out, int ldo, float* state, float* chunk_state,
                              const int* __restrict__ q_start, const int* __restrict__ slot_ids,
                              const float* __restrict__ decay, int heads, int dim, int vdim,
-                             int chunk, int mode, int n_seqs, int n_slots, int* status) {
+                             int chunk, int n_seqs, int n_slots, int* status) {
+  constexpr int mode = OUT ? 0 : 1;
   extern __shared__ __align__(16) float smem[];
   constexpr int VW = kVS * VPT;            // value columns per block
   const int DP = blockDim.y;
@@ -111,22 +112,64 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int 
       S[i][j] = (s_in != nullptr && i < d_per && d < dim && v < vdim) ? s_in[(size_t)d * vdim + v] : 0.f;
     }
   }
+  // FAST (bfloat16, 16-byte aligned rows, one 8-element piece of q, k and v per thread and batch):
+  // the next batch's raw values are fetched into registers while this batch is computed
+  uint4 rq = make_uint4(0, 0, 0, 0), rk = rq, rv = rq;
+  const int q8 = dim / 8, v8n = VW / 8;
+  auto fetch = [&](int tb) {
+    const int nt = min(kTB, t1 - tb);
+    const int tq_ = tid / q8, dq = tid - tq_ * q8;
+    if (tq_ < nt) {
+      const T* row = proj + (size_t)(tb + tq_) * ld + (size_t)h * dim + dq * 8;
+      if (OUT) rq = *reinterpret_cast<const uint4*>(row + q_off);
+      rk = *reinterpret_cast<const uint4*>(row + k_off);
+    }
+    const int tv = tid / v8n, dv_ = tid - tv * v8n;
+    rv = make_uint4(0, 0, 0, 0);
+    if (tv < nt && v0 + dv_ * 8 < vdim)
+      rv = *reinterpret_cast<const uint4*>(proj + (size_t)(tb + tv) * ld + v_off + (size_t)h * vdim + v0 + dv_ * 8);
+  };
+  auto stash = [&](int nt) {
+    const int tq_ = tid / q8, dq = tid - tq_ * q8;
+    if (tq_ < nt) {
+      const __nv_bfloat16* bq = reinterpret_cast<const __nv_bfloat16*>(&rq);
+      const __nv_bfloat16* bk = reinterpret_cast<const __nv_bfloat16*>(&rk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (OUT) q_s[tq_ * dim + dq * 8 + e] = silu_f(__bfloat162float(bq[e]));
+        k_s[tq_ * dim + dq * 8 + e] = silu_f(__bfloat162float(bk[e]));
+      }
+    }
+    const int tv = tid / v8n, dv_ = tid - tv * v8n;
+    if (tv < nt) {
+      const __nv_bfloat16* bv = reinterpret_cast<const __nv_bfloat16*>(&rv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v_s[tv * VW + dv_ * 8 + e] = silu_f(__bfloat162float(bv[e]));
+    }
+  };
+  if (FAST && t0 < t1) fetch(t0);
   for (int tb = t0; tb < t1; tb += kTB) {
     const int nt = min(kTB, t1 - tb);
     __syncthreads();
-    for (int i = tid; i < nt * dim; i += nthreads) {
-      const int tt = i / dim, d = i - tt * dim;
-      const T* row = proj + (size_t)(tb + tt) * ld + (size_t)h * dim + d;
-      q_s[tt * dim + d] = silu_f(to_float<T>(row[q_off]));
-      k_s[tt * dim + d] = silu_f(to_float<T>(row[k_off]));
+    if (FAST) {
+      stash(nt);
+      __syncthreads();
+      if (tb + kTB < t1) fetch(tb + kTB);
+    } else {
+      for (int i = tid; i < nt * dim; i += nthreads) {
+        const int tt = i / dim, d = i - tt * dim;
+        const T* row = proj + (size_t)(tb + tt) * ld + (size_t)h * dim + d;
+        if (OUT) q_s[tt * dim + d] = silu_f(to_float<T>(row[q_off]));
+        k_s[tt * dim + d] = silu_f(to_float<T>(row[k_off]));
+      }
+      for (int i = tid; i < nt * VW; i += nthreads) {
+        const int tt = i / VW, vv = i - tt * VW;
+        v_s[i] = v0 + vv < vdim
+                     ? silu_f(to_float<T>(proj[(size_t)(tb + tt) * ld + v_off + (size_t)h * vdim + v0 + vv]))
+                     : 0.f;
+      }
+      __syncthreads();
     }
-    for (int i = tid; i < nt * VW; i += nthreads) {
-      const int tt = i / VW, vv = i - tt * VW;
-      v_s[i] = v0 + vv < vdim
-                   ? silu_f(to_float<T>(proj[(size_t)(tb + tt) * ld + v_off + (size_t)h * vdim + v0 + vv]))
-                   : 0.f;
-    }
-    __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
       float vt[VPT], acc[VPT];
 #pragma unroll
@@ -139,16 +182,20 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int 
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         if (i < d_per && d0 + i < dim) {
-          const float kv = kk[i], qv = qq[i];
+          const float kv = kk[i];
 #pragma unroll
-          for (int j = 0; j < VPT; ++j) {
-            S[i][j] = fmaf(dec, S[i][j], kv * vt[j]);
-            acc[j] = fmaf(S[i][j], qv, acc[j]);
+          for (int j = 0; j < VPT; ++j) S[i][j] = fmaf(dec, S[i][j], kv * vt[j]);
+          if (OUT) {
+            const float qv = qq[i];
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) acc[j] = fmaf(S[i][j], qv, acc[j]);
           }
         }
       }
+      if (OUT) {
 #pragma unroll
-      for (int j = 0; j < VPT; ++j) part[(ty * kTB + tt) * VW + j * kVS + tx] = acc[j];
+        for (int j = 0; j < VPT; ++j) part[(ty * kTB + tt) * VW + j * kVS + tx] = acc[j];
+      }
     }
     if (mode == 0) {
       __syncthreads();
@@ -253,43 +300,54 @@ extern "C" int leone_linear_attention(int dtype, const void* proj, int ld, int q
   const size_t smem = sizeof(float) * ((size_t)2 * kTB * dim + kTB * vw + (size_t)dp * kTB * vw);
   const int vslices = (vdim + vw - 1) / vw;
   if (smem > 200 * 1024) return kRefusedSize;
-#define SCAN(T, D, V, GRIDZ, MODE)                                                                         \
+  // the prefetching form: bfloat16, rows and offsets 16-byte aligned, one piece a thread and batch
+  const int nthreads = kVS * dp;
+  const bool fast = dtype == 1 && dim % 8 == 0 && vdim % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 &&
+                    v_off % 8 == 0 && ((uintptr_t)proj % 16) == 0 && kTB * (dim / 8) <= nthreads &&
+                    kTB * (vw / 8) <= nthreads;
+#define SCAN(T, D, V, GRIDZ, OUT, FAST)                                                                    \
   do {                                                                                                     \
-    auto kern = linear_attention_scan_kernel<T, D, V>;                                                     \
+    auto kern = linear_attention_scan_kernel<T, D, V, OUT, FAST>;                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     kern<<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(                                            \
         (const T*)proj, ld, q_off, k_off, v_off, out, ldo, state, chunk_state, q_start, slot_ids, decay,   \
-        heads, dim, vdim, chunk, MODE, n_seqs, n_slots, status);                                           \
+        heads, dim, vdim, chunk, n_seqs, n_slots, status);                                                 \
   } while (0)
-#define SCAN_D(T, GRIDZ, MODE)                                      \
+#define SCAN_F(T, D, V, GRIDZ, OUT)                                     \
+  do {                                                                  \
+    if (fast && sizeof(T) == 2) SCAN(T, D, V, GRIDZ, OUT, true);        \
+    else SCAN(T, D, V, GRIDZ, OUT, false);                              \
+  } while (0)
+#define SCAN_D(T, GRIDZ, OUT)                                       \
   do {                                                              \
     if (vpt == 4) {                                                 \
-      if (dpt == 8) SCAN(T, 8, 4, GRIDZ, MODE);                     \
-      else if (dpt == 16) SCAN(T, 16, 4, GRIDZ, MODE);              \
-      else SCAN(T, 32, 4, GRIDZ, MODE);                             \
+      if (dpt == 8) SCAN_F(T, 8, 4, GRIDZ, OUT);                    \
+      else if (dpt == 16) SCAN_F(T, 16, 4, GRIDZ, OUT);             \
+      else SCAN_F(T, 32, 4, GRIDZ, OUT);                            \
     } else {                                                        \
-      if (dpt == 8) SCAN(T, 8, 1, GRIDZ, MODE);                     \
-      else if (dpt == 16) SCAN(T, 16, 1, GRIDZ, MODE);              \
-      else if (dpt == 32) SCAN(T, 32, 1, GRIDZ, MODE);              \
-      else SCAN(T, 64, 1, GRIDZ, MODE);                             \
+      if (dpt == 8) SCAN_F(T, 8, 1, GRIDZ, OUT);                    \
+      else if (dpt == 16) SCAN_F(T, 16, 1, GRIDZ, OUT);             \
+      else if (dpt == 32) SCAN_F(T, 32, 1, GRIDZ, OUT);             \
+      else SCAN_F(T, 64, 1, GRIDZ, OUT);                            \
     }                                                               \
   } while (0)
-#define SCAN_T(GRIDZ, MODE)                             \
+#define SCAN_T(GRIDZ, OUT)                              \
   do {                                                  \
-    if (dtype == 0) SCAN_D(float, GRIDZ, MODE);         \
-    else SCAN_D(__nv_bfloat16, GRIDZ, MODE);            \
+    if (dtype == 0) SCAN_D(float, GRIDZ, OUT);          \
+    else SCAN_D(__nv_bfloat16, GRIDZ, OUT);             \
   } while (0)
   if (dtype != 0 && dtype != 1) return kRefusedDtype;
   if (chunk == 0) {
-    SCAN_T(n_seqs, 0);
+    SCAN_T(n_seqs, true);
     return launch_result();
   }
-  SCAN_T(n_chunks, 1);
+  SCAN_T(n_chunks, false);
   const size_t per_seq = (size_t)heads * dim * vdim;
   linear_attention_chunk_prefix_kernel<<<dim3((unsigned)((per_seq + 255) / 256), n_seqs), 256, 0, stream>>>(
       chunk_state, state, q_start, slot_ids, decay, heads, dim, vdim, chunk, n_seqs, n_slots);
-  SCAN_T(n_chunks, 0);
+  SCAN_T(n_chunks, true);
 #undef SCAN_T
+#undef SCAN_F
 #undef SCAN_D
 #undef SCAN
   return launch_result();

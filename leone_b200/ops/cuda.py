@@ -484,7 +484,8 @@ class CudaOps:
                 _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions),
                 n, heads, dk, dv, c_float(scale), int(window or 0), _ptr(sink), 0 if sink is None else _dt(sink.dtype),
                 _ptr(gate), 0 if gate is None else gate.stride(0), cache.page_tokens, kp.shape[0], bt.shape[0],
-                splits, _ptr(partial), _ptr(ctx.status), self._stream()), "attention_latent_mma")
+                splits, _ptr(partial), 1 if os.environ.get("LEONE_NO_SHARED_KEY_TILES", "0") == "1" else 0,
+                _ptr(ctx.status), self._stream()), "attention_latent_mma")
             return
         _check(self.mixers.leone_attention_latent(
             _dt(q_abs.dtype), _ptr(q_abs), _ptr(out), _ptr(kp), _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token),
