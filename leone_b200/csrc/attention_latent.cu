@@ -46,6 +46,8 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int dkv_off
                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                       const int* __restrict__ block_table, int table_width, int n_seqs, T* __restrict__ pool,
                       int num_pages, int page_tokens, int* status) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ __align__(16) float smem[];
   float* cs = smem;                 // [rot_dims/2][2]
   __shared__ float scratch[33];
@@ -99,6 +101,8 @@ attention_latent_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
                         int dk, int dv, float scale, int window, const TS* __restrict__ sink,
                         const T* __restrict__ gate, int ldg, int page_tokens, int num_pages, int n_seqs,
                         int* status) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ __align__(16) float smem[];
   long long* off_s = (long long*)smem;                // [128] row index into the pool
   float* p_s = smem + 2 * kLatThreads;                // [128]
@@ -195,7 +199,7 @@ extern "C" int leone_latent_prepare(int dtype, const void* proj, int ld, int q_o
   if (pool != nullptr && (page_tokens <= 0 || table_width <= 0)) return kRefusedSize;
   const size_t smem = sizeof(float) * (size_t)(rot_dims + 2);
 #define PREP(T, TW)                                                                                          \
-  latent_prepare_kernel<T, TW><<<n_tokens, kLatThreads, smem, stream>>>(                                     \
+  launch_kernel(latent_prepare_kernel<T, TW>, dim3(n_tokens), dim3(kLatThreads), smem, stream,                                      \
       (const T*)proj, ld, q_off, dkv_off, (T*)q_abs, heads, dim, rot_dim, rank, (const TW*)norm_w, eps,    \
       freqs, rot_dims, magnitude, adjacent, positions, seq_of_token, block_table, table_width, n_seqs,     \
       (T*)pool, num_pages, page_tokens, status)
@@ -223,7 +227,7 @@ extern "C" int leone_attention_latent(int dtype, const void* q, void* out, const
   const size_t smem = (size_t)(dk + kLatThreads) * sizeof(float) + kLatThreads * sizeof(long long) + 8;
   if (smem > 48 * 1024) return kRefusedSize;
 #define ATT(T, TS, A)                                                                                       \
-  attention_latent_kernel<T, TS, A><<<grid, kLatThreads, smem, stream>>>(                                   \
+  launch_kernel(attention_latent_kernel<T, TS, A>, grid, dim3(kLatThreads), smem, stream,                                    \
       (const T*)q, (T*)out, (const T*)pool, block_table, table_width, seq_of_token, positions, heads, dk, \
       dv, scale, window, (const TS*)sink, (const T*)gate, ldg, page_tokens, num_pages, n_seqs, status)
 #define ATT_A(T, TS)                          \

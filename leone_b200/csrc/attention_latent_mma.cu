@@ -59,6 +59,8 @@ attention_latent_mma_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
                             int window, const TS* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
                             int page_tokens, int num_pages, int n_seqs, int splits, float* __restrict__ partial,
                             int* status) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   constexpr int dv = 32 * NT;
   constexpr int kThreads = kMmaThreads * G;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -319,6 +321,8 @@ __global__ void __launch_bounds__(128)
 attention_latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int heads, int dv,
                               int splits, const TS* __restrict__ sink, const __nv_bfloat16* __restrict__ gate,
                               int ldg) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int groups = (heads + 15) / 16;
   const float* base = partial + (((size_t)t * groups + h / 16) * splits) * 16 * (dv + 2) + (size_t)(h % 16) * (dv + 2);
@@ -375,7 +379,7 @@ extern "C" int leone_attention_latent_mma(const void* q, void* out, const void* 
   do {                                                                                                        \
     auto kern = attention_latent_mma_kernel<TS, N, GG>;                                                       \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                       \
-    kern<<<grid, kMmaThreads * GG, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,              \
+    launch_kernel(kern, grid, dim3(kMmaThreads * GG), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,              \
                                                    (const __nv_bfloat16*)pool, block_table, table_width,     \
                                                    seq_of_token, positions, n_tokens, heads, dk, scale,      \
                                                    window, (const TS*)sink, (const __nv_bfloat16*)gate, ldg, \
@@ -404,10 +408,10 @@ extern "C" int leone_attention_latent_mma(const void* q, void* out, const void* 
   if (splits > 1) {
     const dim3 mgrid(n_tokens, heads);
     if (sink_dtype == 0)
-      attention_latent_merge_kernel<float><<<mgrid, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, heads, dv, splits,
+      launch_kernel(attention_latent_merge_kernel<float>, mgrid, dim3(128), 0, stream, partial, (__nv_bfloat16*)out, heads, dv, splits,
                                                                       (const float*)sink, (const __nv_bfloat16*)gate, ldg);
     else
-      attention_latent_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(
+      launch_kernel(attention_latent_merge_kernel<__nv_bfloat16>, mgrid, dim3(128), 0, stream, 
           partial, (__nv_bfloat16*)out, heads, dv, splits, (const __nv_bfloat16*)sink, (const __nv_bfloat16*)gate, ldg);
   }
   return launch_result();

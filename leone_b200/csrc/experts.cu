@@ -21,6 +21,8 @@ __device__ __forceinline__ float silu_e(float z) { return z / (1.f + expf(-z)); 
 __global__ void __launch_bounds__(128)
 select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int experts, int top, int softmax,
               int renormalize, int* __restrict__ chosen, float* __restrict__ weight) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
@@ -69,6 +71,8 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
 __global__ void __launch_bounds__(1024)
 group_pairs_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __restrict__ offsets,
                    int* __restrict__ order) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ int count_s[];      // [experts] counts, then cursors
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count_s[e] = 0;
   __syncthreads();
@@ -122,6 +126,8 @@ experts_gate_up_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w
                        T* __restrict__ act, const int* __restrict__ offsets, const int* __restrict__ order,
                        const float* __restrict__ weight, int experts, int top, int width, int ff,
                        int scale_input) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   __shared__ float As[GK][GM + 4];
   __shared__ float Gs[GK][GN + 4];
   __shared__ float Us[GK][GN + 4];
@@ -199,6 +205,8 @@ __global__ void __launch_bounds__(256)
 experts_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, float* __restrict__ pair_out,
                     const int* __restrict__ offsets, const int* __restrict__ order,
                     const float* __restrict__ weight, int experts, int width, int ff, int scale_input) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   __shared__ float As[GK][GM + 4];
   __shared__ float Ws[GK][GN + 4];
   int expert, row0, row1;
@@ -260,6 +268,8 @@ experts_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, flo
 // hidden[t, :] += sum_j pair_out[t * top + j, :], j ascending
 __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* __restrict__ pair_out,
                                        long long total, int width, int top) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / width;
@@ -300,6 +310,8 @@ experts_gate_up_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const _
                            const int* __restrict__ offsets, const int* __restrict__ order,
                            const float* __restrict__ weight, int experts, int top, int width, int ff,
                            int scale_input) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_m[];
   __shared__ int a_index[TM];
   __shared__ float a_weight[TM];
@@ -349,6 +361,8 @@ experts_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat
                         float* __restrict__ pair_out, const int* __restrict__ offsets,
                         const int* __restrict__ order, const float* __restrict__ weight, int experts, int width,
                         int ff, int scale_input) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_m[];
   __shared__ int a_index[TM];
   __shared__ int a_pair[TM];
@@ -394,7 +408,7 @@ extern "C" int leone_experts_select(const float* logits, int ldl, int n_tokens, 
                                     int renormalize, int* chosen, float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048 || ldl < experts) return kRefusedSize;
-  select_kernel<<<(n_tokens + 3) / 4, 128, sizeof(float) * 4 * (size_t)experts, stream>>>(
+  launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)experts, stream, 
       logits, ldl, n_tokens, experts, top, softmax, renormalize, chosen, weight);
   return launch_result();
 }
@@ -410,7 +424,7 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
   if (width <= 0 || ff <= 0 || experts <= 0 || top <= 0 || experts > 8192) return kRefusedSize;
   const long long pairs = (long long)n_tokens * top;
   if (pairs > (1 << 30)) return kRefusedSize;
-  group_pairs_kernel<<<1, 1024, sizeof(int) * (size_t)experts, stream>>>(chosen, (int)pairs, experts, offsets, order);
+  launch_kernel(group_pairs_kernel, dim3(1), dim3(1024), sizeof(int) * (size_t)experts, stream, chosen, (int)pairs, experts, offsets, order);
   if (tensor_cores && dtype == 1 && width % 8 == 0 && ff % 8 == 0 && ldx % 8 == 0) {
     const long long tiles = (pairs + TM - 1) / TM + (experts < pairs ? experts : pairs);
     if (tiles > 65535) return kRefusedSize;
@@ -421,15 +435,15 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
       cudaFuncSetAttribute(experts_down_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
       configured = true;
     }
-    experts_gate_up_mma_kernel<<<dim3((ff + TN - 1) / TN, (unsigned)tiles), 128, smem_up, stream>>>(
+    launch_kernel(experts_gate_up_mma_kernel, dim3((ff + TN - 1) / TN, (unsigned)tiles), dim3(128), smem_up, stream, 
         (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, (__nv_bfloat16*)act,
         offsets, order, weight, experts, top, width, ff, scale_input);
-    experts_down_mma_kernel<<<dim3((width + TN - 1) / TN, (unsigned)tiles), 128, smem_down, stream>>>(
+    launch_kernel(experts_down_mma_kernel, dim3((width + TN - 1) / TN, (unsigned)tiles), dim3(128), smem_down, stream, 
         (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, pair_out, offsets, order, weight, experts, width, ff,
         scale_input);
     const long long total = (long long)n_tokens * width;
     const long long blocks = (total + 255) / 256;
-    experts_combine_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(hidden, pair_out,
+    launch_kernel(experts_combine_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, hidden, pair_out,
                                                                                                 total, width, top);
     return launch_result();
   }
@@ -438,17 +452,17 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
   if (max_tiles > 65535) return kRefusedSize;
   const dim3 grid_up((ff + GN - 1) / GN, (unsigned)max_tiles), grid_down((width + GN - 1) / GN, (unsigned)max_tiles);
   if (dtype == 0) {
-    experts_gate_up_kernel<float><<<grid_up, 256, 0, stream>>>((const float*)x, ldx, (const float*)w_gate,
+    launch_kernel(experts_gate_up_kernel<float>, grid_up, dim3(256), 0, stream, (const float*)x, ldx, (const float*)w_gate,
                                                                (const float*)w_up, (float*)act, offsets, order,
                                                                weight, experts, top, width, ff, scale_input);
-    experts_down_kernel<float><<<grid_down, 256, 0, stream>>>((const float*)act, (const float*)w_down, pair_out,
+    launch_kernel(experts_down_kernel<float>, grid_down, dim3(256), 0, stream, (const float*)act, (const float*)w_down, pair_out,
                                                               offsets, order, weight, experts, width, ff,
                                                               scale_input);
   } else if (dtype == 1) {
-    experts_gate_up_kernel<__nv_bfloat16><<<grid_up, 256, 0, stream>>>(
+    launch_kernel(experts_gate_up_kernel<__nv_bfloat16>, grid_up, dim3(256), 0, stream, 
         (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up,
         (__nv_bfloat16*)act, offsets, order, weight, experts, top, width, ff, scale_input);
-    experts_down_kernel<__nv_bfloat16><<<grid_down, 256, 0, stream>>>(
+    launch_kernel(experts_down_kernel<__nv_bfloat16>, grid_down, dim3(256), 0, stream, 
         (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, pair_out, offsets, order, weight, experts, width,
         ff, scale_input);
   } else {
@@ -456,7 +470,7 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
   }
   const long long total = (long long)n_tokens * width;
   const long long blocks = (total + 255) / 256;
-  experts_combine_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(hidden, pair_out, total,
+  launch_kernel(experts_combine_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, hidden, pair_out, total,
                                                                                               width, top);
   return launch_result();
 }

@@ -42,6 +42,8 @@ linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int 
                              const int* __restrict__ q_start, const int* __restrict__ slot_ids,
                              const float* __restrict__ decay, int heads, int dim, int vdim,
                              int chunk, int n_seqs, int n_slots, int* status) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   constexpr int mode = OUT ? 0 : 1;
   extern __shared__ __align__(16) float smem[];
   constexpr int VW = kVS * VPT;            // value columns per block
@@ -231,6 +233,8 @@ __global__ void linear_attention_chunk_prefix_kernel(float* chunk_state, const f
                                                      const int* __restrict__ slot_ids,
                                                      const float* __restrict__ decay, int heads, int dim,
                                                      int vdim, int chunk, int n_seqs, int n_slots) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   const int s = blockIdx.y;
   const size_t per_seq = (size_t)heads * dim * vdim;
   const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -259,6 +263,8 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(256)
 gate_norm_kernel(const float* __restrict__ o, int width, const TW* __restrict__ w, const T* __restrict__ gate,
                  int ldg, T* __restrict__ out, float eps) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const float* row = o + (size_t)t * width;
@@ -309,7 +315,7 @@ extern "C" int leone_linear_attention(int dtype, const void* proj, int ld, int q
   do {                                                                                                     \
     auto kern = linear_attention_scan_kernel<T, D, V, OUT, FAST>;                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    kern<<<dim3(vslices, heads, GRIDZ), block, smem, stream>>>(                                            \
+    launch_kernel(kern, dim3(vslices, heads, GRIDZ), block, smem, stream,                                             \
         (const T*)proj, ld, q_off, k_off, v_off, out, ldo, state, chunk_state, q_start, slot_ids, decay,   \
         heads, dim, vdim, chunk, n_seqs, n_slots, status);                                                 \
   } while (0)
@@ -343,7 +349,7 @@ extern "C" int leone_linear_attention(int dtype, const void* proj, int ld, int q
   }
   SCAN_T(n_chunks, false);
   const size_t per_seq = (size_t)heads * dim * vdim;
-  linear_attention_chunk_prefix_kernel<<<dim3((unsigned)((per_seq + 255) / 256), n_seqs), 256, 0, stream>>>(
+  launch_kernel(linear_attention_chunk_prefix_kernel, dim3((unsigned)((per_seq + 255) / 256), n_seqs), dim3(256), 0, stream, 
       chunk_state, state, q_start, slot_ids, decay, heads, dim, vdim, chunk, n_seqs, n_slots);
   SCAN_T(n_chunks, true);
 #undef SCAN_T
@@ -360,7 +366,7 @@ extern "C" int leone_gate_norm(int dtype, const float* o, int n_tokens, int widt
   if (n_tokens <= 0) return 0;
   if (width <= 0) return kRefusedSize;
 #define GN(T, TW) \
-  gate_norm_kernel<T, TW><<<n_tokens, 256, 0, stream>>>(o, width, (const TW*)w, (const T*)gate, ldg, (T*)out, eps)
+  launch_kernel(gate_norm_kernel<T, TW>, dim3(n_tokens), dim3(256), 0, stream, o, width, (const TW*)w, (const T*)gate, ldg, (T*)out, eps)
   if (dtype == 0 && w_dtype == 0) GN(float, float);
   else if (dtype == 1 && w_dtype == 0) GN(__nv_bfloat16, float);
   else if (dtype == 1 && w_dtype == 1) GN(__nv_bfloat16, __nv_bfloat16);

@@ -11,6 +11,8 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(256)
 rms_norm_pair_kernel(const float* __restrict__ x, const TW* __restrict__ w_a, const TW* __restrict__ w_b,
                      T* __restrict__ out_a, T* __restrict__ out_b, int width, float eps) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * width;
   float ss = 0.f;
@@ -26,6 +28,8 @@ rms_norm_pair_kernel(const float* __restrict__ x, const TW* __restrict__ w_a, co
 
 template <typename T>
 __global__ void relu_squared_kernel(T* __restrict__ x, long long n) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float v = fmaxf(to_float<T>(x[i]), 0.f);
     x[i] = from_float<T>(v * v);
@@ -40,6 +44,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_batched_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __restrict__ C, int M, int N, int K,
                     int lda, int ldw, int ldc, long long a_bs, long long w_bs, long long c_bs) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   A += (size_t)blockIdx.z * a_bs;
@@ -96,6 +102,8 @@ __global__ void __launch_bounds__(128)
 gemm_batched_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                         __nv_bfloat16* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc, long long a_bs,
                         long long w_bs, long long c_bs) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_m[];
   __shared__ int a_index[TM];
   A += (size_t)blockIdx.z * a_bs;
@@ -129,12 +137,14 @@ gemm_batched_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
 
 using namespace leone;
 
+extern "C" void leone_mixers_set_pdl(int enabled) { pdl_flag() = enabled ? 1 : 0; }
+
 extern "C" int leone_rms_norm_pair(const float* x, const void* w_a, const void* w_b, int w_dtype, void* out_a,
                                    void* out_b, int out_dtype, int n, int width, float eps, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (width <= 0) return kRefusedSize;
 #define NP(T, TW)                                                                                            \
-  rms_norm_pair_kernel<T, TW><<<n, 256, 0, stream>>>(x, (const TW*)w_a, (const TW*)w_b, (T*)out_a, (T*)out_b, \
+  launch_kernel(rms_norm_pair_kernel<T, TW>, dim3(n), dim3(256), 0, stream, x, (const TW*)w_a, (const TW*)w_b, (T*)out_a, (T*)out_b, \
                                                      width, eps)
   if (out_dtype == 0 && w_dtype == 0) NP(float, float);
   else if (out_dtype == 1 && w_dtype == 0) NP(__nv_bfloat16, float);
@@ -149,8 +159,8 @@ extern "C" int leone_relu_squared(int dtype, void* x, long long n, cudaStream_t 
   if (n <= 0) return 0;
   const long long want = (n + 255) / 256;
   const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
-  if (dtype == 0) relu_squared_kernel<float><<<blocks, 256, 0, stream>>>((float*)x, n);
-  else if (dtype == 1) relu_squared_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)x, n);
+  if (dtype == 0) launch_kernel(relu_squared_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, n);
+  else if (dtype == 1) launch_kernel(relu_squared_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, n);
   else return kRefusedDtype;
   return launch_result();
 }
@@ -173,15 +183,15 @@ extern "C" int leone_gemm_batched(int dtype, const void* a, const void* w, void*
       cudaFuncSetAttribute(gemm_batched_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       configured = true;
     }
-    gemm_batched_mma_kernel<<<tgrid, 128, smem, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+    launch_kernel(gemm_batched_mma_kernel, tgrid, dim3(128), smem, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
                                                           (__nv_bfloat16*)c, m, n, k, lda, ldw, ldc, a_bs, w_bs, c_bs);
     return launch_result();
   }
   if (dtype == 0)
-    gemm_batched_kernel<float><<<grid, 256, 0, stream>>>((const float*)a, (const float*)w, (float*)c, m, n, k, lda,
+    launch_kernel(gemm_batched_kernel<float>, grid, dim3(256), 0, stream, (const float*)a, (const float*)w, (float*)c, m, n, k, lda,
                                                          ldw, ldc, a_bs, w_bs, c_bs);
   else if (dtype == 1)
-    gemm_batched_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+    launch_kernel(gemm_batched_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
                                                                  (__nv_bfloat16*)c, m, n, k, lda, ldw, ldc, a_bs,
                                                                  w_bs, c_bs);
   else

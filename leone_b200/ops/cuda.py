@@ -106,7 +106,14 @@ class CudaOps:
     def set_pdl(self, enabled: bool) -> None:
         """Programmatic dependent launch: a kernel may start (and fetch weights) while its
         predecessor in the stream still runs; it waits before touching the step's data."""
+        self._pdl = bool(enabled)
+        # The kernels of the 'mixers' module call the same two instructions, but are launched without
+        # the attribute unless LEONE_MIXERS_PDL=1: with it a decode step of the hybrid design measured
+        # slower (1.15 ms against 1.04), a prompt step about the same (7.3 ms against 7.5).
+        self._mixers_pdl = os.environ.get("LEONE_MIXERS_PDL", "0") == "1"
         self.core.leone_core_set_pdl(1 if enabled else 0)
+        if self.__dict__.get("_mixers") is not None:
+            self._mixers.leone_mixers_set_pdl(1 if enabled and self._mixers_pdl else 0)
         if self.fast is not None:
             self.fast.lib.leone_bf16_set_pdl(1 if enabled else 0)
 
@@ -366,6 +373,7 @@ class CudaOps:
         lib = self.__dict__.get("_mixers")
         if lib is None:
             lib = self.__dict__["_mixers"] = ctypes.CDLL(ensure_built("mixers"))
+            lib.leone_mixers_set_pdl(1 if self._pdl and self._mixers_pdl else 0)
         return lib
 
     def rms_norm_pair(self, x, w_a, w_b, out_a, out_b, eps):
