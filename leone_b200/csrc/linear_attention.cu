@@ -36,7 +36,7 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 // A thread owns VPT value columns of DPT rows of the state, so a k or q element read from shared
 // memory serves VPT multiply-adds.
 template <typename T, int DPT, int VPT, bool OUT, bool FAST>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (DPT * VPT <= 64) ? 2 : 1)      // two blocks an SM where the state fits 128 registers
 linear_attention_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                              float* __restrict__ out, int ldo, float* state, float* chunk_state,
                              const int* __restrict__ q_start, const int* __restrict__ slot_ids,

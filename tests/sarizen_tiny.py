@@ -50,13 +50,13 @@ TINY = {
          "mlp": {"kind": "dense", "ff": 100}}]},
     # head sizes the tensor-core paths like (64), a window of 32 over pages of 16, more experts
     "R": {"architecture": "Sarizen", "vocab": 256, "width": 128, "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": [
-        {"type": "latent_attention", "mixer": latent(4, 64, 32, 64, 64, 0.1, window=32, base=50000.0,
-                                                     scaling={"factor": 8.0, "original": 128, "fast": 32.0, "slow": 1.0}),
+        {"type": "latent_attention", "mixer": latent(4, 64, 32, 64, 64, 0.1, window=32, base=20000.0,
+                                                     scaling={"factor": 5.0, "original": 128, "fast": 24.0, "slow": 2.0}),
          "mlp": moe(64, 8, 2, 64)},
         {"type": "lightning", "mixer": lightning(4, 64, 64, [0.6, 0.9, 0.99, 0.999]), "mlp": {"kind": "dense", "ff": 256}}]},
     # 18 heads (two groups of query rows on the tensor-core attention), no window on one latent layer,
     # value width 128, keys of 80 and 144 elements, a wide lightning head
-    "S": {"architecture": "Sarizen", "vocab": 200, "width": 96, "norm": {"eps": 1e-6}, "logit_scale": 0.25, "layers": [
+    "S": {"architecture": "Sarizen", "vocab": 200, "width": 96, "norm": {"eps": 2e-6}, "logit_scale": 0.75, "layers": [
         {"type": "latent_attention", "mixer": latent(18, 16, 16, 8, 64, 0.2, base=1000.0, dims=8), "mlp": None},
         {"type": "lightning", "mixer": lightning(2, 136, 40, [0.8, 0.99]), "mlp": moe(24, 6, 6, 16)},
         {"type": "latent_attention", "mixer": latent(5, 32, 16, 32, 128, 0.12, window=70, scaling=YARN),

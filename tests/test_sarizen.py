@@ -71,7 +71,7 @@ def test_config_rejections():
 
 def test_yarn_frequencies_agree_with_the_plain_formula():
     from leone_b200.parts.rotary import scaled_frequencies
-    for dims, base, scaling in ((16, 50000.0, {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
+    for dims, base, scaling in ((24, 30000.0, {"factor": 6.0, "original": 1024, "fast": 16.0, "slow": 2.0}),
                                 (4, 10000.0, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}),
                                 (12, 100.0, None), (64, 1e6, {"factor": 40.0, "original": 4096, "fast": 32, "slow": 1})):
         f, mag = scaled_frequencies(dims, base, scaling)
