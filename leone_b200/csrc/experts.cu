@@ -63,7 +63,8 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
     total += best;
     __syncwarp();
   }
-  if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
+  if (renormalize)
+    for (int j = lane; j < top; j += 32) weight[(size_t)t * top + j] /= total;
 }
 
 // One block: counts per expert, their prefix sums, and every pair's row among its expert's.
@@ -407,7 +408,7 @@ using namespace leone;
 extern "C" int leone_experts_select(const float* logits, int ldl, int n_tokens, int experts, int top, int softmax,
                                     int renormalize, int* chosen, float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048 || ldl < experts) return kRefusedSize;
+  if (experts <= 0 || top <= 0 || top > experts || experts > 2048 || ldl < experts) return kRefusedSize;
   launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)experts, stream, 
       logits, ldl, n_tokens, experts, top, softmax, renormalize, chosen, weight);
   return launch_result();

@@ -125,6 +125,22 @@ def test_replay_on_the_gpu(which, dtype, mode):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("switch", ["LEONE_NO_LATENT_MMA", "LEONE_NO_EXPERT_MMA", "LEONE_NO_SHARED_KEY_TILES",
+                                    "LEONE_MIXERS_PDL", "LEONE_NO_TENSOR_CORES"])
+@pytest.mark.parametrize("which", ["R", "S"])
+def test_bfloat16_kernel_switches(which, switch, monkeypatch):
+    """Every bfloat16 kernel has an any-size form behind a switch; with the switch thrown the same
+    traces still agree with the plain implementation (prompt portions of 100 tokens and decode)."""
+    monkeypatch.setenv(switch, "1")
+    tensors = tiny_tensors(which)
+    reqs = _requests(TINY[which]["vocab"], [130, 40, 75])
+    steps = replay.trace_portions(reqs, sizes=(100, 2, 1, 1, 30)) + []
+    eng = _engine(which, tensors, "bfloat16", "cuda:0", max_tokens=replay.max_live_tokens(steps), max_batch_tokens=128)
+    out = replay.run_trace_engine(eng, steps)
+    replay.compare(steps, out, _plain(which, tensors, True), reqs, what=f"{which} with {switch}", **BF16)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("which,layer", [("P", 0), ("P", 1), ("P", 2), ("P", 3), ("Q", 0), ("Q", 1), ("Q", 2)])
 def test_each_layer_alone(which, layer):
     """A model of one layer: its mixer and feed-forward with nothing else to hide behind."""
