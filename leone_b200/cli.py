@@ -146,10 +146,10 @@ def cmd_doctor(args) -> int:
             return 1
         print(f"architecture: {config.architecture}")
         for key, value in config.to_json_dict().items():
-            if key != "architectures":
+            if key not in ("architectures", "architecture"):
                 print(f"  {key}: {value}")
-        print(f"context limit: {config.max_position_embeddings} tokens")
         spec = spec_from_config(config)
+        print(f"context limit: {spec.max_positions} tokens")
         model = Model(spec, Runtime("cpu", torch.float32, None, 0))
         try:
             ckpt = Checkpoint(args.model)
@@ -197,7 +197,10 @@ def cmd_replay(args, rest) -> int:
 
 
 def cmd_bench(args) -> int:
-    from .benchmark import run, serving
+    from .benchmark import compare_designs, run, serving
+    if args.design:
+        return compare_designs(args.design, args.size, steps=min(args.steps, 64), warmup=max(3, args.warmup),
+                               batch=args.batch, context=args.context or 2048)
     if args.workload == "serving":
         return serving(args.shape or "qwen3-1.7b", requests=args.requests, new_tokens=args.new_tokens,
                        prefill_chunk=args.prefill_chunk, layers=args.layers)
@@ -275,7 +278,7 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--store-dtype", choices=["float32", "bfloat16"], default="bfloat16")
     sub.add_parser("replay", help="same options as bin/trace_run", add_help=False)
-    b = sub.add_parser("bench", help="decode/prefill throughput of a Qwen3-8B-shaped model")
+    b = sub.add_parser("bench", help="decode/prefill throughput of a Qwen3-8B-shaped model (--design: another design beside it)")
     b.add_argument("--steps", type=int, default=256)
     b.add_argument("--warmup", type=int, default=3)
     b.add_argument("--layers", type=int, default=None)
@@ -286,6 +289,9 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--workload", choices=["decode", "serving"], default="decode",
                    help="decode: device-timed decode and prefill; serving: many requests through the scheduler")
     b.add_argument("--requests", type=int, default=64)
+    b.add_argument("--design", choices=["sarizen"], default=None,
+                   help="another design at real layer sizes beside the dense decoder at equal size")
+    b.add_argument("--size", choices=["small", "medium"], default="small")
     b.add_argument("--new-tokens", type=int, default=128)
     b.add_argument("--prefill-chunk", type=int, default=1024)
     return ap
