@@ -326,35 +326,40 @@ experts_gate_up_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const _
     a_weight[r] = (ok && scale_input) ? weight[pair] : 1.f;
   }
   __syncthreads();
-  float acc[2][8][4];
+  float acc[2][2][4][4];
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[m][mt][n][i] = 0.f;
   grouped_mainloop<2>(smem_m, x, a_index, ldx, w_gate + ((size_t)expert * ff + n0) * width,
                       w_up + ((size_t)expert * ff + n0) * width, min(TN, ff - n0), width, acc);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int wm = warp >> 1, wn = warp & 1;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = warp * 16 + g + 8 * i;
-    if (row0 + r >= row1) continue;
-    const float w = a_weight[r];
+  for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int col = n0 + n * 8 + 2 * tq;
-      if (col >= ff) continue;
-      float v[2];
+    for (int i = 0; i < 2; ++i) {
+      const int r = wm * 32 + mt * 16 + g + 8 * i;
+      if (row0 + r >= row1) continue;
+      const float w = a_weight[r];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const float gg = round_to<__nv_bfloat16>(acc[0][n][2 * i + j] * w);
-        const float uu = round_to<__nv_bfloat16>(acc[1][n][2 * i + j] * w);
-        v[j] = silu_e(gg) * uu;
+      for (int n = 0; n < 4; ++n) {
+        const int col = n0 + wn * 32 + n * 8 + 2 * tq;
+        if (col >= ff) continue;
+        float v[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float gg = round_to<__nv_bfloat16>(acc[0][mt][n][2 * i + j] * w);
+          const float uu = round_to<__nv_bfloat16>(acc[1][mt][n][2 * i + j] * w);
+          v[j] = silu_e(gg) * uu;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(act + (size_t)(row0 + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
       }
-      *reinterpret_cast<__nv_bfloat162*>(act + (size_t)(row0 + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
     }
-  }
 }
 
 __global__ void __launch_bounds__(128)
@@ -376,28 +381,33 @@ experts_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat
     a_pair[r] = ok ? order[row0 + r] : 0;
   }
   __syncthreads();
-  float acc[1][8][4];
+  float acc[1][2][4][4];
 #pragma unroll
-  for (int n = 0; n < 8; ++n)
+  for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[0][n][i] = 0.f;
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[0][mt][n][i] = 0.f;
   grouped_mainloop<1>(smem_m, act, a_index, ff, w_down + ((size_t)expert * width + n0) * ff, nullptr,
                       min(TN, width - n0), ff, acc);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int wm = warp >> 1, wn = warp & 1;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = warp * 16 + g + 8 * i;
-    if (row0 + r >= row1) continue;
-    const int pair = a_pair[r];
-    const float f = scale_input ? 1.f : weight[pair];
+  for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int col = n0 + n * 8 + 2 * tq;
-      if (col >= width) continue;
-      *reinterpret_cast<float2*>(pair_out + (size_t)pair * width + col) =
-          make_float2(acc[0][n][2 * i] * f, acc[0][n][2 * i + 1] * f);
+    for (int i = 0; i < 2; ++i) {
+      const int r = wm * 32 + mt * 16 + g + 8 * i;
+      if (row0 + r >= row1) continue;
+      const int pair = a_pair[r];
+      const float f = scale_input ? 1.f : weight[pair];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = n0 + wn * 32 + n * 8 + 2 * tq;
+        if (col >= width) continue;
+        *reinterpret_cast<float2*>(pair_out + (size_t)pair * width + col) =
+            make_float2(acc[0][mt][n][2 * i] * f, acc[0][mt][n][2 * i + 1] * f);
+      }
     }
-  }
 }
 
 }  // namespace leone

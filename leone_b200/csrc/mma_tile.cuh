@@ -1,6 +1,7 @@
 // A 64 x 64 output tile of C = A B^T on tensor cores (bfloat16 operands, fp32 sums), shared by the
-// grouped products of the routed experts and the product batched over heads.  Four warps of 16 rows
-// each; operands come through a three-stage cp.async ring in shared memory (rows of 32 k-values,
+// grouped products of the routed experts and the product batched over heads.  Four warps of 32 rows x
+// 32 columns each (thread's element [m][mt][nt][2i+j]: row (warp/2)*32 + mt*16 + lane/4 + 8i, column
+// (warp%2)*32 + nt*8 + 2*(lane%4) + j); operands come through a three-stage cp.async ring in shared memory (rows of 32 k-values,
 // padded so that ldmatrix finds eight rows in eight different banks).  Rows of A are found through
 // an index (gathered rows; a negative index is a row of zeros); rows of B are K elements apart.
 #pragma once
@@ -30,7 +31,7 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
 template <int NB>
 __device__ __forceinline__ void grouped_mainloop(unsigned char* smem, const __nv_bfloat16* a_base, const int* a_index_s,
                                                  int lda, const __nv_bfloat16* b0_base, const __nv_bfloat16* b1_base,
-                                                 int n_valid, int K, float (*acc)[8][4], int ldb = 0) {
+                                                 int n_valid, int K, float (*acc)[2][4][4], int ldb = 0) {
   if (ldb == 0) ldb = K;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kStageBytes = (TM + NB * TN) * TPITCH;
@@ -57,7 +58,9 @@ __device__ __forceinline__ void grouped_mainloop(unsigned char* smem, const __nv
     if (s < kblocks) load(s, s);
     else asm volatile("cp.async.commit_group;" ::: "memory");
   }
-  const int mi = lane >> 3;
+  // the warps are 2 x 2, each with 32 rows x 32 columns (of every B matrix): two A fragments and
+  // two B fragment pairs a matrix serve eight MMAs a matrix
+  const int mi = lane >> 3, wm = warp >> 1, wn = warp & 1;
   for (int kb = 0; kb < kblocks; ++kb) {
     asm volatile("cp.async.wait_group %0;" ::"n"(TSTAGES - 2) : "memory");
     __syncthreads();
@@ -66,16 +69,23 @@ __device__ __forceinline__ void grouped_mainloop(unsigned char* smem, const __nv
     const uint32_t st = base + (kb % TSTAGES) * kStageBytes;
 #pragma unroll
     for (int ks = 0; ks < TK / 16; ++ks) {
-      uint32_t a0, a1, a2, a3;
-      ldsm4(st + (warp * 16 + (lane & 15)) * TPITCH + (lane >> 4) * 16 + ks * 32, a0, a1, a2, a3);
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldsm4(st + (wm * 32 + mt * 16 + (lane & 15)) * TPITCH + (lane >> 4) * 16 + ks * 32, a[mt][0], a[mt][1], a[mt][2],
+              a[mt][3]);
 #pragma unroll
       for (int m = 0; m < NB; ++m) {
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
+        for (int np = 0; np < 2; ++np) {
           uint32_t b0, b1, b2, b3;
-          ldsm4(st + (TM + m * TN + np * 16 + (lane & 7) + (mi >> 1) * 8) * TPITCH + (mi & 1) * 16 + ks * 32, b0, b1, b2, b3);
-          mma16816(acc[m][2 * np], a0, a1, a2, a3, b0, b1);
-          mma16816(acc[m][2 * np + 1], a0, a1, a2, a3, b2, b3);
+          ldsm4(st + (TM + m * TN + wn * 32 + np * 16 + (lane & 7) + (mi >> 1) * 8) * TPITCH + (mi & 1) * 16 + ks * 32, b0,
+                b1, b2, b3);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma16816(acc[m][mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+            mma16816(acc[m][mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+          }
         }
       }
     }

@@ -112,25 +112,30 @@ gemm_batched_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
   for (int r = threadIdx.x; r < TM; r += 128) a_index[r] = m0 + r < M ? m0 + r : -1;
   __syncthreads();
-  float acc[1][8][4];
+  float acc[1][2][4][4];
 #pragma unroll
-  for (int n = 0; n < 8; ++n)
+  for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[0][n][i] = 0.f;
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[0][mt][n][i] = 0.f;
   grouped_mainloop<1>(smem_m, A, a_index, lda, W + (size_t)n0 * ldw, nullptr, min(TN, N - n0), K, acc, ldw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int wm = warp >> 1, wn = warp & 1;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int m = m0 + warp * 16 + g + 8 * i;
-    if (m >= M) continue;
+  for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int col = n0 + n * 8 + 2 * tq;
-      if (col >= N) continue;
-      *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + col) =
-          __floats2bfloat162_rn(acc[0][n][2 * i], acc[0][n][2 * i + 1]);
+    for (int i = 0; i < 2; ++i) {
+      const int m = m0 + wm * 32 + mt * 16 + g + 8 * i;
+      if (m >= M) continue;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = n0 + wn * 32 + n * 8 + 2 * tq;
+        if (col >= N) continue;
+        *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + col) =
+            __floats2bfloat162_rn(acc[0][mt][n][2 * i], acc[0][mt][n][2 * i + 1]);
+      }
     }
-  }
 }
 
 }  // namespace leone
