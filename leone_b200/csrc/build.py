@@ -32,8 +32,10 @@ MODULES: Dict[str, List[str]] = {
     # the bfloat16 serving path: tensor-core products and tiled attention
     "bf16": ["gemm_tc.cu", "gemm_pair.cu", "attention_tiled.cu", "attention_prefill_pingpong.cu"],
     # mixers and feed-forwards beyond softmax attention over K/V pages and the dense gated layer:
-    # linear attention with a decaying state, attention through a cached latent, routed experts
-    "mixers": ["linear_attention.cu", "attention_latent.cu", "attention_latent_mma.cu", "experts.cu", "norm_act.cu"],
+    # linear attention with a decaying state, attention through a cached latent, attention with a choice
+    # of mask and weight rule, routed experts
+    "mixers": ["linear_attention.cu", "attention_latent.cu", "attention_latent_mma.cu", "attention_masked.cu",
+               "experts.cu", "norm_act.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
     # the host side of the runtime (pages, block tables, step metadata, the scheduler's decisions,

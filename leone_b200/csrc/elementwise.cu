@@ -151,6 +151,33 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// The gated layer with its gate's shape as parameters:
+//   g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' * sigmoid(slope * g') * (u' + shift)
+// (limit = +inf: no clamping).  slope 1, no limit and shift 0 are SwiGLU.
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n, int inter, float slope,
+                                 float limit, float shift) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / inter, col = i - row * inter;
+    const float g = fminf(to_float<T>(gate_up[row * 2 * inter + col]), limit);
+    const float u = fminf(fmaxf(to_float<T>(gate_up[row * 2 * inter + inter + col]), -limit), limit);
+    out[i] = from_float<T>(g / (1.f + expf(-slope * g)) * (u + shift));
+  }
+}
+
+// fp32 rows into the run dtype (or a plain copy), for operands that are made from the residual stream.
+template <typename T>
+__global__ void convert_kernel(const float* __restrict__ in, T* __restrict__ out, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = from_float<T>(in[i]);
+}
+
 // ---------------------------------------------------------------------------
 // Per-head q/k RMSNorm + rotary + paged cache write, one warp per
 // (token, head) of the fused qkv row [q heads | k heads | v heads]
@@ -615,6 +642,32 @@ extern "C" int leone_swiglu(int dtype, const void* gate_up, void* out, int n, in
   else
     return kRefusedDtype;
   return launch_result();
+}
+
+extern "C" int leone_gated_act(int dtype, const void* gate_up, void* out, int n, int inter, float slope, float limit,
+                               float shift, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (inter <= 0 || !(limit > 0.f)) return kRefusedSize;
+  const size_t total = (size_t)n * inter;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == 0)
+    return launch_kernel(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up,
+                         (float*)out, n, inter, slope, limit, shift);
+  if (dtype == 1)
+    return launch_kernel(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n, inter, slope, limit, shift);
+  return kRefusedDtype;
+}
+
+extern "C" int leone_convert(int out_dtype, const float* in, void* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long want = (n + 255) / 256;
+  const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (out_dtype == 0)
+    return launch_kernel(convert_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, (float*)out, n);
+  if (out_dtype == 1)
+    return launch_kernel(convert_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, in, (__nv_bfloat16*)out, n);
+  return kRefusedDtype;
 }
 
 extern "C" int leone_qk_norm_rope_write(

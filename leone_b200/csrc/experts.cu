@@ -3,7 +3,11 @@
 //   z = W_router x (an fp32 product of the framework's own),  s = sigmoid(z) or softmax(z),  the `top` largest s are chosen
 //   (lowest index first on equal scores); a pair's weight is its s, optionally divided by the sum
 //   of the chosen.  The weight multiplies the expert's input (`scale_input`) or its output.
-//   expert_e(a) = W_down_e (silu(W_gate_e a) * (W_up_e a))
+//   Optionally the choice is restricted to the best groups: the experts form `groups` equal runs of
+//   neighbours, a run is worth its largest score, only experts of the `keep` best runs (the lowest
+//   index among equal ones) can be chosen; and the chosen weights are multiplied by `weight_scale`.
+//   expert_e(a) = W_down_e (silu(W_gate_e a) * (W_up_e a)), or, without a gate matrix,
+//   expert_e(a) = W_down_e max(W_up_e a, 0)^2
 //   out[t] += sum over the token's pairs, in the order of choice.
 //
 // Nothing is read back by the host: the pairs are counted and placed per expert on the device, and
@@ -20,7 +24,8 @@ __device__ __forceinline__ float silu_e(float z) { return z / (1.f + expf(-z)); 
 // One warp per token: scores from the router's fp32 logits, then the `top` largest.
 __global__ void __launch_bounds__(128)
 select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int experts, int top, int softmax,
-              int renormalize, int* __restrict__ chosen, float* __restrict__ weight) {
+              int renormalize, int groups, int keep, float weight_scale, int* __restrict__ chosen,
+              float* __restrict__ weight) {
   pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -41,6 +46,24 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
     for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-row[e]));
   }
   __syncwarp();
+  if (groups > 1 && keep < groups) {
+    // what every group is worth, then the groups that are not kept lose their experts
+    float* worth = smem + (size_t)4 * experts + (size_t)warp * groups;
+    const int per = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float w = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) w = fmaxf(w, sc[e]);
+      worth[g] = w;
+    }
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+      int better = 0;             // groups that come before this one: worth more, or the same at a lower index
+      for (int o = 0; o < groups; ++o) better += (worth[o] > worth[g] || (worth[o] == worth[g] && o < g)) ? 1 : 0;
+      if (better >= keep)
+        for (int e = g * per; e < (g + 1) * per; ++e) sc[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
   float total = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -65,6 +88,10 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
   }
   if (renormalize)
     for (int j = lane; j < top; j += 32) weight[(size_t)t * top + j] /= total;
+  if (weight_scale != 1.f) {
+    __syncwarp();
+    for (int j = lane; j < top; j += 32) weight[(size_t)t * top + j] *= weight_scale;
+  }
 }
 
 // One block: counts per expert, their prefix sums, and every pair's row among its expert's.
@@ -163,7 +190,7 @@ experts_gate_up_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w
     for (int i = 0; i < 4; ++i) {
       const int k = k0 + wk + i;
       const bool ok = w_ok && k < width;
-      Gs[wk + i][wr] = ok ? to_float<T>(g_row[k]) : 0.f;
+      Gs[wk + i][wr] = (ok && w_gate != nullptr) ? to_float<T>(g_row[k]) : 0.f;
       Us[wk + i][wr] = ok ? to_float<T>(u_row[k]) : 0.f;
     }
     __syncthreads();
@@ -194,7 +221,11 @@ experts_gate_up_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < ff) act[(size_t)r * ff + n] = from_float<T>(silu_e(round_to<T>(g[i][j])) * round_to<T>(u[i][j]));
+      if (n >= ff) continue;
+      const float uu = round_to<T>(u[i][j]);
+      // without a gate matrix the expert is ungated: the squared ReLU of its one product
+      act[(size_t)r * ff + n] = from_float<T>(w_gate != nullptr ? silu_e(round_to<T>(g[i][j])) * uu
+                                                                : fmaxf(uu, 0.f) * fmaxf(uu, 0.f));
     }
   }
 }
@@ -362,6 +393,55 @@ experts_gate_up_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const _
     }
 }
 
+// The ungated expert's first product with the squared ReLU in the epilogue.
+__global__ void __launch_bounds__(128)
+experts_up_mma_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w_up,
+                      __nv_bfloat16* __restrict__ act, const int* __restrict__ offsets,
+                      const int* __restrict__ order, int experts, int top, int width, int ff) {
+  pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char smem_m[];
+  __shared__ int a_index[TM];
+  int expert, row0, row1;
+  if (!find_tile_m(offsets, experts, blockIdx.y, expert, row0, row1)) return;
+  const int n0 = blockIdx.x * TN;
+  for (int r = threadIdx.x; r < TM; r += 128) {
+    const bool ok = row0 + r < row1;
+    a_index[r] = ok ? order[row0 + r] / top : -1;
+  }
+  __syncthreads();
+  float acc[1][2][4][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[0][mt][n][i] = 0.f;
+  grouped_mainloop<1>(smem_m, x, a_index, ldx, w_up + ((size_t)expert * ff + n0) * width, nullptr,
+                      min(TN, ff - n0), width, acc);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int wm = warp >> 1, wn = warp & 1;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = wm * 32 + mt * 16 + g + 8 * i;
+      if (row0 + r >= row1) continue;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = n0 + wn * 32 + n * 8 + 2 * tq;
+        if (col >= ff) continue;
+        float v[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float uu = fmaxf(round_to<__nv_bfloat16>(acc[0][mt][n][2 * i + j]), 0.f);
+          v[j] = uu * uu;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(act + (size_t)(row0 + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
+      }
+    }
+}
+
 __global__ void __launch_bounds__(128)
 experts_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down,
                         float* __restrict__ pair_out, const int* __restrict__ offsets,
@@ -415,15 +495,20 @@ experts_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat
 using namespace leone;
 
 // logits: fp32 [n_tokens, ldl] (the router's product); chosen, weight: [n_tokens * top].
+// groups <= 1 (or keep == groups): every expert can be chosen.
 extern "C" int leone_experts_select(const float* logits, int ldl, int n_tokens, int experts, int top, int softmax,
-                                    int renormalize, int* chosen, float* weight, cudaStream_t stream) {
+                                    int renormalize, int groups, int keep, float weight_scale, int* chosen,
+                                    float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || top <= 0 || top > experts || experts > 2048 || ldl < experts) return kRefusedSize;
-  launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)experts, stream, 
-      logits, ldl, n_tokens, experts, top, softmax, renormalize, chosen, weight);
+  if (groups < 1) groups = 1;
+  if (experts % groups != 0 || keep < 1 || keep > groups || top > experts / groups * keep) return kRefusedSize;
+  launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)(experts + groups), stream,
+      logits, ldl, n_tokens, experts, top, softmax, renormalize, groups, keep, weight_scale, chosen, weight);
   return launch_result();
 }
 
+// w_gate null: ungated experts (see the top of the file).
 // x: [n_tokens, ldx]; chosen, weight: [n_tokens * top]; scratch: offsets int [experts + 1], order int
 // [pairs], act [pairs, ff] in the run dtype, pair_out fp32 [pairs, width]; hidden fp32 [n_tokens, width].
 extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const void* w_gate, const void* w_up,
@@ -433,6 +518,7 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
                                      cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (width <= 0 || ff <= 0 || experts <= 0 || top <= 0 || experts > 8192) return kRefusedSize;
+  if (w_gate == nullptr && scale_input) return kRefusedSize;      // an ungated expert is weighted at its output
   const long long pairs = (long long)n_tokens * top;
   if (pairs > (1 << 30)) return kRefusedSize;
   launch_kernel(group_pairs_kernel, dim3(1), dim3(1024), sizeof(int) * (size_t)experts, stream, chosen, (int)pairs, experts, offsets, order);
@@ -444,8 +530,14 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
     if (!configured) {
       cudaFuncSetAttribute(experts_gate_up_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
       cudaFuncSetAttribute(experts_down_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+      cudaFuncSetAttribute(experts_up_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
       configured = true;
     }
+    if (w_gate == nullptr)
+      launch_kernel(experts_up_mma_kernel, dim3((ff + TN - 1) / TN, (unsigned)tiles), dim3(128), smem_down, stream,
+          (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_up, (__nv_bfloat16*)act, offsets, order, experts, top,
+          width, ff);
+    else
     launch_kernel(experts_gate_up_mma_kernel, dim3((ff + TN - 1) / TN, (unsigned)tiles), dim3(128), smem_up, stream, 
         (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, (__nv_bfloat16*)act,
         offsets, order, weight, experts, top, width, ff, scale_input);

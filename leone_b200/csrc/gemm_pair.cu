@@ -423,7 +423,7 @@ extern "C" int leone_gemm_pair(const void* x, const void* w, void* out, const fl
                                int ldx, int ldw, int ldc, int epilogue, int width, int splits, float* workspace,
                                int* status, int sm_count, void* norm_out_x, const float* norm_out_w,
                                float* norm_out_ss, int ld_norm_out, const float* norm_in_ss, int norm_in_parts,
-                               float norm_eps, cudaStream_t stream) {
+                               float norm_eps, const float* gate_shape, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || (k % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return kRefusedAlignment;
   if (epilogue < 0 || epilogue > 3 || sm_count < 2 || width < 32 || width > 256 || (width % 16) != 0) return kRefusedSize;
@@ -447,6 +447,7 @@ extern "C" int leone_gemm_pair(const void* x, const void* w, void* out, const fl
   if (r != 0) return r;
   GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, 0, workspace, nullptr, status, nullptr,
                (__nv_bfloat16*)norm_out_x, norm_out_w, norm_out_ss, ld_norm_out, norm_in_ss, norm_in_parts, norm_eps, 0};
+  set_gate_shape(p, gate_shape);
   return launch_pair(mw, mx, p, width, sm_count, stream);
 }
 

@@ -59,7 +59,19 @@ struct GemmParams {
   int norm_in_parts;
   float norm_eps;
   int l2_ahead;      // k-blocks of weights past the early stages that the producer asks the L2 for
+  // The gate's shape of epilogue 3: g' sigmoid(slope g') (u' + shift) with g' = min(g, limit) and
+  // u' = clamp(u, -limit, limit).  gate_plain: slope 1, no limit, shift 0 (SwiGLU).
+  int gate_plain;
+  float gate_slope, gate_limit, gate_shift;
 };
+
+// Host side: the four gate fields from an optional {slope, limit, shift} (null: SwiGLU).
+inline void set_gate_shape(GemmParams& p, const float* shape) {
+  p.gate_plain = shape == nullptr ? 1 : 0;
+  p.gate_slope = shape == nullptr ? 1.f : shape[0];
+  p.gate_limit = shape == nullptr ? INFINITY : shape[1];
+  p.gate_shift = shape == nullptr ? 0.f : shape[2];
+}
 
 __device__ __forceinline__ long long global_ns() {
   long long t;
@@ -86,6 +98,13 @@ __device__ __forceinline__ Unit unit_of(int u, const GemmParams& p) {
 // and division (a few units in the last place of fp32, far below the rounding to bf16; e^-g = inf
 // gives g * 0).
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+// The same with the gate's shape from the parameters (a block-uniform branch).
+__device__ __forceinline__ float gate_mul(const GemmParams& p, float g, float u) {
+  if (p.gate_plain) return silu_mul(g, u);
+  g = fminf(g, p.gate_limit);
+  u = fminf(fmaxf(u, -p.gate_limit), p.gate_limit);
+  return __fdividef(g, 1.f + __expf(-p.gate_slope * g)) * (u + p.gate_shift);
+}
 
 // Swapped orientation: the thread that owns weight row n finishes NC token columns
 // m0 + c .. m0 + c + NC - 1 whose sums are in v (r: the residual values, fetched by the caller
@@ -112,7 +131,7 @@ __device__ __forceinline__ void finish_swapped(const GemmParams& p, float (&v)[N
       const float x = __shfl_xor_sync(0xffffffffu, low ? v[j + 1] : v[j], 16);
       const float g = low ? v[j] : x, u = low ? x : v[j + 1];
       const int m = m0 + c + j + (low ? 0 : 1);
-      if (n < p.N && m < p.M) ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] = __float2bfloat16_rn(silu_mul(g, u));
+      if (n < p.N && m < p.M) ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + col] = __float2bfloat16_rn(gate_mul(p, g, u));
     }
     return;
   }
@@ -192,8 +211,8 @@ __device__ __forceinline__ void finish_token_major32(const GemmParams& p, float 
     uint32_t packed[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float a = silu_mul(v[2 * j], v[16 + 2 * j]);
-      const float b = silu_mul(v[2 * j + 1], v[16 + 2 * j + 1]);
+      const float a = gate_mul(p, v[2 * j], v[16 + 2 * j]);
+      const float b = gate_mul(p, v[2 * j + 1], v[16 + 2 * j + 1]);
       __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
       packed[j] = *reinterpret_cast<uint32_t*>(&v2);
     }
@@ -307,8 +326,8 @@ __device__ __forceinline__ void finish_token_major_row(const GemmParams& p, uint
         uint32_t packed[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float a = silu_mul(g[2 * j], u[2 * j]);
-          const float b = silu_mul(g[2 * j + 1], u[2 * j + 1]);
+          const float a = gate_mul(p, g[2 * j], u[2 * j]);
+          const float b = gate_mul(p, g[2 * j + 1], u[2 * j + 1]);
           __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
           packed[j] = *reinterpret_cast<uint32_t*>(&v2);
         }

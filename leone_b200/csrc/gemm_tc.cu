@@ -711,7 +711,8 @@ extern "C" int leone_gemm_tc_cluster_capacity_token_major(int splits) {
 
 // x: [m, k] bf16 (row stride ldx), w: [n, k] bf16 (row stride ldw), out: [m, n] (row stride ldc).
 // epilogue 0: bf16 out; 1: fp32 out; 2: fp32 out = acc + residual (same layout as out);
-// 3: w holds interleaved gate/up rows, out is bf16 [m, n/2] = silu(gate) * up.
+// 3: w holds interleaved gate/up rows, out is bf16 [m, n/2] = silu(gate) * up; gate_shape (host
+// floats {slope, limit, shift}, or null) gives the gate another shape (see GemmParams).
 // The first `full_tiles` tiles (in the kernel's tile order) are computed whole; the others have K
 // split `splits` ways.  splits > 1 needs `workspace` (fp32) and zeroed `counters` of the sizes
 // leone_gemm_tc_scratch gives for (tiles - full_tiles).  More than 256 tokens are never split.
@@ -734,7 +735,7 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
                              int full_tiles, float* workspace, int* counters, int* status,
                              int sm_count, int cluster, int token_major, void* norm_out_x, const float* norm_out_w,
                              float* norm_out_ss, int ld_norm_out, const float* norm_in_ss,
-                             int norm_in_parts, float norm_eps, cudaStream_t stream) {
+                             int norm_in_parts, float norm_eps, const float* gate_shape, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || (k % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return kRefusedAlignment;
   if (epilogue < 0 || epilogue > 3 || splits < 1 || sm_count < 1) return kRefusedSize;
@@ -769,6 +770,7 @@ extern "C" int leone_gemm_tc(const void* x, const void* w, void* out, const floa
   GemmParams p{out, residual, m, n, k, ldc, epilogue, splits, full_tiles, workspace, counters, status,
                g_gemm_trace, (__nv_bfloat16*)norm_out_x, norm_out_w, norm_out_ss, ld_norm_out, norm_in_ss,
                norm_in_parts, norm_eps, (swap && bn <= 16) ? g_l2_ahead : 0};
+  set_gate_shape(p, gate_shape);
   if (g_gemm_trace != nullptr) g_gemm_trace += g_gemm_trace_stride;
   if (!swap && cluster) return launch_gemm<256, false, true>(mw, mx, p, sm_count, stream);
   if (!swap && tm_width == 240) return launch_gemm<240, false>(mw, mx, p, sm_count, stream);

@@ -17,7 +17,7 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers built-in parts)
 from ..parts.base import FixedState, PagedKV, Runtime, WeightSpec
 from ..parts.spec import ModelSpec
-from ..registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+from ..registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, POSITION_ENCODINGS,
                         spec_from_config)
 
 
@@ -82,12 +82,25 @@ class Model:
         es, hs = spec.embedding_spec(), spec.head_spec()
         self.embedding = EMBEDDINGS.get(es.kind)(dict(es.params), rt)
         self.head = HEADS.get(hs.kind)(dict(hs.params), rt)
+        # parts between layers: run position -> part; equal specs are one part
+        self.injections = {}
+        self._injection_parts = []
+        for pos, ps in spec.injections:
+            for seen, part in self._injection_parts:
+                if seen == ps:
+                    break
+            else:
+                part = INJECTIONS.get(ps.kind)({"hidden_size": spec.hidden_size, **ps.params}, rt)
+                self._injection_parts.append((ps, part))
+            self.injections[pos] = part
 
     # -- weights ----------------------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
         specs = list(self.embedding.weight_specs())
         for holder in self._holders:
             specs += holder.full_specs()
+        for _, part in self._injection_parts:
+            specs += part.weight_specs()
         specs += self.final_norm.weight_specs()
         specs += self.head.weight_specs()
         return specs
@@ -109,6 +122,8 @@ class Model:
         self.embedding.load({w.name: tensors.pop(w.name) for w in self.embedding.weight_specs()})
         for holder in self._holders:
             holder.load(tensors)
+        for _, part in self._injection_parts:
+            part.load({w.name: tensors.pop(w.name) for w in part.weight_specs()})
         self.final_norm.load({s.final_norm_name: tensors.pop(s.final_norm_name)})
         self.head.load({w.name: tensors.pop(w.name) for w in self.head.weight_specs()}, self.embedding)
 
@@ -141,6 +156,7 @@ class Model:
             for part in (block.mixer, block.feed_forward, *getattr(block, "extra_parts", {}).values()):
                 if part is not None and hasattr(part, "weight_bytes"):
                     total += part.weight_bytes()
+        total += sum(part.weight_bytes() for part in self.injections.values())
         total += self.head.weight_bytes()
         return total
 
@@ -156,13 +172,16 @@ class Model:
                                    *getattr(b, "extra_parts", {}).values()) if p is not None)
                      for b in self.blocks]
         total += max(per_layer, default=0)
+        if self.injections:
+            total += max_tokens * self.hidden_size * 4 + sum(p.scratch_bytes(max_tokens) for _, p in self._injection_parts)
         total += max_logit_rows * (self.vocab_size * 4 + self.hidden_size * item)
         ops_scratch = getattr(self.rt.ops, "scratch_bytes", None)
         return total + (ops_scratch() if ops_scratch is not None else 0)
 
     def load_transient_bytes(self) -> int:
         """The most any one part holds beyond its inputs while it loads."""
-        parts = [h.part for h in self._holders] + [self.embedding, self.head, self.final_norm]
+        parts = [h.part for h in self._holders] + [self.embedding, self.head, self.final_norm] + \
+            [p for _, p in self._injection_parts]
         return max((p.load_transient_bytes() for p in parts), default=0)
 
     # -- forward ----------------------------------------------------------------------
@@ -181,16 +200,27 @@ class Model:
         rt = self.rt
         hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
         self.embedding.forward(ctx, hidden)
+        origin = None
+        if self.injections:
+            # what the embedding left, for the parts that feed it in again between layers
+            origin = rt.buffer("stream_origin", ctx.n_tokens, self.hidden_size, torch.float32)
+            rt.ops.convert(hidden, origin)
+            for _, part in self._injection_parts:
+                part.begin_step(ctx)
         order = self.spec.run_order
         pre = None           # the entry norm of the next block, if the last product before it folded it in
         for pos, idx in enumerate(order):
             block = self.blocks[idx]
+            if pos in self.injections:
+                self.injections[pos].forward(ctx, hidden, origin)
+                pre = None       # a norm folded into the product before it was of the stream as it was
             if not getattr(block, "chains_norms", False):
                 block.forward(ctx, ctx.cache_view(pos), hidden)
                 pre = None
                 continue
             after = None
-            if pos + 1 < len(order) and getattr(self.blocks[order[pos + 1]], "chains_norms", False):
+            if pos + 1 < len(order) and pos + 1 not in self.injections and \
+                    getattr(self.blocks[order[pos + 1]], "chains_norms", False):
                 after = self.blocks[order[pos + 1]].entry_norm(ctx, hidden)
             pre = block.forward(ctx, ctx.cache_view(pos), hidden, pre=pre, after=after)
         return self.logits(ctx, hidden)

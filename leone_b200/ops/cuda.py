@@ -261,28 +261,45 @@ class CudaOps:
             return
         self._gemm_simt(x, w.weight, out, epilogue, residual)
 
-    def linear_swiglu(self, x, w_gate_up: PreparedMatrix, out, norm_in=None):
-        """``out = silu(x @ gate.T) * (x @ up.T)`` for a matrix from ``prepare_gate_up``."""
+    def linear_swiglu(self, x, w_gate_up: PreparedMatrix, out, norm_in=None, gate_shape=None):
+        """``out = silu(x @ gate.T) * (x @ up.T)`` for a matrix from ``prepare_gate_up``.
+        ``gate_shape = (slope, limit, shift)``: ``g' sigmoid(slope g') (u' + shift)`` with
+        ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` (``limit`` may be ``inf``)."""
         m = x.shape[0]
         inter = w_gate_up.out_features // 2
         _need(out.shape == (m, inter) and out.dtype == x.dtype and out.is_contiguous(),
               "linear_swiglu: output shape")
+        _need(gate_shape is None or (len(gate_shape) == 3 and gate_shape[1] > 0), "linear_swiglu: gate shape")
         if m == 0:
             return
         if norm_in is not None:
             ni, _ = self._norm_args(m, w_gate_up, norm_in, None)
-            _need(self.fast.linear_swiglu(x, w_gate_up, out, ni), "linear_swiglu: fused norm off the tensor-core path")
+            _need(self.fast.linear_swiglu(x, w_gate_up, out, ni, gate_shape),
+                  "linear_swiglu: fused norm off the tensor-core path")
             self.launches += 1
             return
-        if self.fast is not None and self.fast.linear_swiglu(x, w_gate_up, out):
+        if self.fast is not None and self.fast.linear_swiglu(x, w_gate_up, out, None, gate_shape):
             self.launches += 1
             return
         _need(getattr(w_gate_up, "gate_up_layout", None) == "stacked", "gate/up layout")
         scratch = self._scratch("gate_up", m, 2 * inter, x.dtype)
         self._gemm_simt(x, w_gate_up.weight, scratch, 0, None)
         self.launches += 1
-        _check(self.core.leone_swiglu(_dt(x.dtype), _ptr(scratch), _ptr(out), m, inter,
-                                      self._stream()), "swiglu")
+        if gate_shape is None:
+            _check(self.core.leone_swiglu(_dt(x.dtype), _ptr(scratch), _ptr(out), m, inter,
+                                          self._stream()), "swiglu")
+        else:
+            slope, limit, shift = gate_shape
+            _check(self.core.leone_gated_act(_dt(x.dtype), _ptr(scratch), _ptr(out), m, inter, c_float(slope),
+                                             c_float(limit), c_float(shift), self._stream()), "gated_act")
+
+    def convert(self, src, out):
+        """``out = src`` elementwise, ``src`` fp32, ``out`` fp32 or the run dtype (same shape)."""
+        _need(src.dtype == torch.float32 and src.is_contiguous() and out.is_contiguous()
+              and src.shape == out.shape, "convert: layout")
+        self.launches += 1
+        _check(self.core.leone_convert(_dt(out.dtype), _ptr(src), _ptr(out), ctypes.c_longlong(src.numel()),
+                                       self._stream()), "convert")
 
     def swiglu(self, gate_up, out):
         m, two_i = gate_up.shape
@@ -366,6 +383,70 @@ class CudaOps:
             _ptr(bt), bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions), n, n_q, n_kv, d,
             c_float(scale), int(window or 0), cache.page_tokens, kp.shape[0], bt.shape[0],
             _ptr(ctx.status), self._stream()), "attention_generic")
+
+    _MASKS = {"causal": 0, "window": 1, "chunk": 2}
+    _WEIGHTS = {"softmax": 0, "softmax_plus_one": 1, "sigmoid": 2}
+
+    def attention_prepare(self, ctx, qkv, n_q, n_kv, dk, dv, norm, q_w, k_w, eps, freqs, pairing, cache):
+        """Norm (``None``, ``"per_head"`` or ``"whole"``; fp32 weights) and rotation (fp32
+        ``freqs`` per pair or None) of q and k in place, and the step's keys and values into
+        their pages (``csrc/attention_masked.cu``).  Row layout ``[q heads x dk | k heads x dk |
+        v heads x dv]``."""
+        n = qkv.shape[0]
+        _need(qkv.stride(1) == 1 and qkv.shape[1] == (n_q + n_kv) * dk + n_kv * dv, "attention_prepare: qkv layout")
+        mode = {None: 0, "per_head": 1, "whole": 2}[norm]
+        if mode:
+            want = (dk, dk) if mode == 1 else (n_q * dk, n_kv * dk)
+            _need(q_w is not None and k_w is not None and q_w.dtype == torch.float32 and k_w.dtype == torch.float32
+                  and q_w.is_contiguous() and k_w.is_contiguous() and (q_w.numel(), k_w.numel()) == want,
+                  "attention_prepare: norm weights")
+        rot = 0
+        if freqs is not None:
+            _need(freqs.dtype == torch.float32 and freqs.is_contiguous() and 2 * freqs.numel() <= dk,
+                  "attention_prepare: frequencies")
+            rot = 2 * freqs.numel()
+        _need(pairing in ("half_split", "adjacent"), f"rotary pairing '{pairing}'")
+        if cache is not None:
+            kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+            _need(vp is not None and kp.is_contiguous() and vp.is_contiguous() and kp.dtype == qkv.dtype == vp.dtype
+                  and kp.shape[1] == n_kv and kp.shape[2] == cache.page_tokens and kp.shape[3] == dk
+                  and vp.shape[3] == dv and bt.dtype == torch.int32 and bt.is_contiguous(), "attention_prepare: cache layout")
+            pool_args = (_ptr(bt), bt.shape[1], bt.shape[0], _ptr(kp), _ptr(vp), kp.shape[0], cache.page_tokens)
+        else:
+            pool_args = (c_void_p(0), 0, ctx.n_seqs, c_void_p(0), c_void_p(0), 0, 0)
+        self.launches += 1
+        _check(self.mixers.leone_attention_prepare(
+            _dt(qkv.dtype), _ptr(qkv), qkv.stride(0), n, n_q, n_kv, dk, dv, mode, _ptr(q_w), _ptr(k_w), c_float(eps),
+            _ptr(freqs), rot, 1 if pairing == "adjacent" else 0, _ptr(ctx.positions), _ptr(ctx.seq_of_token),
+            *pool_args, _ptr(ctx.status), self._stream()), "attention_prepare")
+
+    def attention_masked(self, ctx, qkv, out, n_q, n_kv, dk, dv, scale, mask, mask_size, weights, bias, cache):
+        """Attention with a mask (``"causal"``, ``"window"``, ``"chunk"`` of ``mask_size``) and a
+        weight rule (``"softmax"``, ``"softmax_plus_one"``, ``"sigmoid"`` with a fp32 ``bias`` per
+        head) over key pages of ``dk`` and value pages of ``dv`` elements."""
+        n = qkv.shape[0]
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        _need(out.shape == (n, n_q * dv) and out.is_contiguous() and out.dtype == qkv.dtype and qkv.stride(1) == 1,
+              "attention_masked: output layout")
+        _need(vp is not None and kp.is_contiguous() and vp.is_contiguous() and kp.dtype == qkv.dtype == vp.dtype
+              and kp.shape[1] == n_kv and kp.shape[3] == dk and vp.shape[3] == dv, "attention_masked: cache layout")
+        _need(mask in self._MASKS and weights in self._WEIGHTS, f"attention_masked: mask '{mask}' / weights '{weights}'")
+        if weights == "sigmoid":
+            _need(bias is not None and bias.dtype == torch.float32 and bias.numel() == n_q and bias.is_contiguous(),
+                  "attention_masked: bias")
+        self.launches += 1
+        if self.fast is not None and self.attention_masked_tiled(ctx, qkv, out, n_q, n_kv, dk, dv, scale, mask,
+                                                                 mask_size, weights, bias, cache):
+            return
+        _check(self.mixers.leone_attention_masked(
+            _dt(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt),
+            bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions), n, n_q, n_kv, dk, dv, c_float(scale),
+            self._MASKS[mask], int(mask_size), self._WEIGHTS[weights], _ptr(bias), cache.page_tokens, kp.shape[0],
+            bt.shape[0], _ptr(ctx.status), self._stream()), "attention_masked")
+
+    def attention_masked_tiled(self, ctx, qkv, out, n_q, n_kv, dk, dv, scale, mask, mask_size, weights, bias, cache) -> bool:
+        """The tensor-core form of :meth:`attention_masked` where there is one for these sizes."""
+        return False
 
     # -- mixers and feed-forwards of the 'mixers' module (compiled when a model first needs it) ----
     @property
@@ -501,9 +582,12 @@ class CudaOps:
             0 if sink is None else _dt(sink.dtype), _ptr(gate), 0 if gate is None else gate.stride(0),
             cache.page_tokens, kp.shape[0], bt.shape[0], _ptr(ctx.status), self._stream()), "attention_latent")
 
-    def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False):
+    def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False, groups=1,
+                      groups_kept=None, weight_scale=1.0):
         """Router logits as an fp32 product (bfloat16 operands multiply exactly in fp32), then the
-        scores and the ``top`` best experts of every token (``csrc/experts.cu``)."""
+        scores and the ``top`` best experts of every token (``csrc/experts.cu``), optionally among
+        the experts of the ``groups_kept`` best of ``groups`` groups only; the weights times
+        ``weight_scale``."""
         n, width = x.shape
         if not isinstance(w_router, PreparedMatrix):
             w_router = self.prepare_matrix(w_router)
@@ -514,17 +598,21 @@ class CudaOps:
         self.linear(x, w_router, logits)
         self.launches += 1
         _check(self.mixers.leone_experts_select(_ptr(logits), logits.stride(0), n, experts, top, 1 if softmax else 0,
-                                                1 if renormalize else 0, _ptr(chosen), _ptr(weight), self._stream()),
+                                                1 if renormalize else 0, int(groups), int(groups_kept or groups),
+                                                c_float(weight_scale), _ptr(chosen), _ptr(weight), self._stream()),
                "experts_select")
 
     def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
-        """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``."""
+        """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``.
+        ``w_gate`` None: ungated experts, ``W_down max(W_up a, 0)^2``."""
         n, width = x.shape
-        experts, ff = w_gate.shape[0], w_gate.shape[1]
-        _need(x.stride(1) == 1 and w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+        experts, ff = w_up.shape[0], w_up.shape[1]
+        _need(x.stride(1) == 1 and (w_gate is None or (w_gate.is_contiguous() and w_gate.shape == w_up.shape))
+              and w_up.is_contiguous() and w_down.is_contiguous()
               and tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff)
-              and w_gate.dtype == x.dtype and hidden.dtype == torch.float32 and hidden.is_contiguous()
+              and w_up.dtype == x.dtype and hidden.dtype == torch.float32 and hidden.is_contiguous()
               and hidden.shape == (n, width), "experts_forward layout")
+        _need(w_gate is not None or not scale_input, "experts_forward: ungated experts are weighted at their output")
         pairs = n * top
         cap = rt.max_tokens * top
         offsets = rt.flat_buffer("experts_offsets", experts + 1, torch.int32)

@@ -284,7 +284,7 @@ class FastKernels:
         return (False, *self.choose_splits(m, n, k))
 
     def _gemm(self, x, w, out, epilogue, residual, n_rows, splits=None, full_tiles=0, cluster=False,
-              norm_in=None, norm_out=None, token_major=None) -> bool:
+              norm_in=None, norm_out=None, token_major=None, gate_shape=None) -> bool:
         """``splits=None`` lets :meth:`choose_splits` decide; otherwise tiles from
         ``full_tiles`` on are split ``splits`` ways, summed through a workspace or, with
         ``cluster``, inside a thread-block cluster.
@@ -310,18 +310,20 @@ class FastKernels:
         no = (None, None, None, 0) if norm_out is None else \
             (_ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2]), norm_out[0].stride(0))
         ni = (None, 0, c_float(0.0)) if norm_in is None else (_ptr(norm_in[0]), int(norm_in[1]), c_float(norm_in[2]))
+        # the gate's shape of the gated epilogue: three host floats, or null for SwiGLU
+        gs = None if gate_shape is None else (c_float * 3)(*[float(v) for v in gate_shape])
         if pairs:
             # pairs of SMs on tiles of 256 tokens (gemm_pair.cu)
             code = self.lib.leone_gemm_pair(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                             x.stride(0), w.stride(0), out.stride(0), epilogue, width, splits, _ptr(ws),
-                                            _ptr(self.status), self.sm_count, *no, *ni, self._stream())
+                                            _ptr(self.status), self.sm_count, *no, *ni, gs, self._stream())
             if code != 0:
                 raise RuntimeError(f"gemm_pair refused or failed with code {code} for m={m} n={n_rows} k={k}")
             return True
         code = self.lib.leone_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), m, n_rows, k,
                                       x.stride(0), w.stride(0), out.stride(0), epilogue, splits,
                                       full_tiles, _ptr(ws), _ptr(ct), _ptr(self.status), self.sm_count,
-                                      1 if cluster else 0, 1 if token_major else 0, *no, *ni, self._stream())
+                                      1 if cluster else 0, 1 if token_major else 0, *no, *ni, gs, self._stream())
         if code != 0:
             raise RuntimeError(f"gemm_tc refused or failed with code {code} for m={m} n={n_rows} k={k} "
                                f"splits={splits} cluster={cluster} token_major={token_major}")
@@ -404,10 +406,10 @@ class FastKernels:
         m.gate_up_layout = "stacked"
         return m
 
-    def linear_swiglu(self, x, w, out, norm_in=None) -> bool:
+    def linear_swiglu(self, x, w, out, norm_in=None, gate_shape=None) -> bool:
         if getattr(w, "gate_up_layout", None) != "interleaved16" or not self._tc_ok(x, w.weight, out):
             return False
-        return self._gemm(x, w.weight, out, 3, None, w.out_features, norm_in=norm_in)
+        return self._gemm(x, w.weight, out, 3, None, w.out_features, norm_in=norm_in, gate_shape=gate_shape)
 
     # -- attention ------------------------------------------------------------------------
     def decode_splits(self, n_seqs: int, n_kv: int, g: int, max_ctx: int) -> int:

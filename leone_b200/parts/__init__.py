@@ -1,6 +1,6 @@
 """Parts a layer is built from.  Importing this package registers the built-in kinds."""
-from . import (attention, block, embedding, experts, head, latent_attention, linear_attention, mlp, rms_norm,  # noqa: F401
-               rotary, swiglu)
+from . import (attention, block, embedding, experts, head, injection, latent_attention, linear_attention, mlp,  # noqa: F401
+               rms_norm, rotary, swiglu)
 from .base import (Block, Embedding, FeedForward, FixedState, Head, Mixer, Norm, PagedCacheView, PagedKV, Part,
                    PositionEncoding, Runtime, StateView, WeightSpec)
 from .spec import LayerSpec, ModelSpec, PartSpec

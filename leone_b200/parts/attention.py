@@ -14,6 +14,21 @@ all keys); the reference has no windowed layer.
 Every size is a parameter: number of heads, groups, head size (independent of
 the hidden size), presence of the q/k norm, the position encoding and the
 window.
+
+Further parameters, this part's own (the reference has none of them); with any of them the layer
+runs on the kernels of ``csrc/attention_masked.cu``:
+
+``value_head_dim``: values of another width than queries and keys.
+``mask``: what the query at position ``p`` sees besides ``j <= p``: ``"causal"`` (everything),
+``"window"`` (``p - j < window``) or ``"chunk"`` (``floor(j / chunk) == floor(p / chunk)``, chunks
+counted from position 0 of the sequence).
+``weights``: how scores become weights: ``"softmax"``; ``"softmax_plus_one"`` (``exp(s_j) / (1 +
+sum exp(s_j))``: one more member of score 0 without a value); ``"sigmoid"`` (``sigmoid(s_j +
+b_head)`` for every seen key on its own, nothing normalised; ``b`` is the tensor ``bias_name``).
+``qk_norm = "whole"``: one RMS norm over all of a token's query heads together (weight
+``[heads * head_dim]``, multiplied directly) and one over its key heads, before rotation.
+A position encoding that offers ``frequencies()`` instead of a table (``rotary_computed``): the
+kernel forms the angles in fp32, on the first ``rotary_dim`` elements of a head.
 """
 from __future__ import annotations
 
@@ -38,9 +53,21 @@ class Attention(Mixer):
         self.d = int(params["head_dim"])
         if self.n_q % self.n_kv:
             raise ValueError(f"num_heads {self.n_q} is not a multiple of num_kv_heads {self.n_kv}")
-        self.qk_norm = bool(params.get("qk_norm", False))
+        self.dv = int(params.get("value_head_dim") or self.d)
+        norm = params.get("qk_norm", False)
+        self.qk_norm = bool(norm)
+        self.norm_whole = norm == "whole"
         self.eps = float(params.get("qk_norm_eps", 1e-6))
         self.window = params.get("window")
+        self.chunk = params.get("chunk")
+        self.mask = params.get("mask") or ("window" if self.window else "causal")
+        self.weights = params.get("weights", "softmax")
+        if self.mask not in ("causal", "window", "chunk") or self.weights not in ("softmax", "softmax_plus_one", "sigmoid"):
+            raise ValueError(f"attention: mask '{self.mask}' / weights '{self.weights}'")
+        if (self.mask == "window") != bool(self.window) or (self.mask == "chunk") != bool(self.chunk):
+            raise ValueError(f"attention: mask '{self.mask}' with window {self.window} and chunk {self.chunk}")
+        self.bias_name = params.get("bias_name", "bias")
+        self.bias = None
         self.scale = float(params.get("scale", 1.0 / math.sqrt(self.d)))
         pe_name = params.get("position_encoding")
         self.pos = (position_encodings or {}).get(pe_name) if pe_name else None
@@ -50,16 +77,24 @@ class Attention(Mixer):
         self.q_norm_name = params.get("q_norm_name", "q_norm.weight")
         self.k_norm_name = params.get("k_norm_name", "k_norm.weight")
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
-        self.qkv_cols = (self.n_q + 2 * self.n_kv) * self.d
+        self.qkv_cols = (self.n_q + self.n_kv) * self.d + self.n_kv * self.dv
+        # the layer as the reference has it runs on the kernels tuned for it; anything else on the general ones
+        self.general = (self.dv != self.d or self.mask == "chunk" or self.weights != "softmax" or self.norm_whole
+                        or (self.pos is not None and hasattr(self.pos, "frequencies")))
+        if self.general and self.pos is not None and not hasattr(self.pos, "frequencies"):
+            raise ValueError("attention: the general kernels take a position encoding that offers its frequencies")
 
     def weight_specs(self):
         specs = [WeightSpec(self.names["q"], (self.n_q * self.d, self.hidden)),
                  WeightSpec(self.names["k"], (self.n_kv * self.d, self.hidden)),
-                 WeightSpec(self.names["v"], (self.n_kv * self.d, self.hidden)),
-                 WeightSpec(self.names["o"], (self.hidden, self.n_q * self.d))]
+                 WeightSpec(self.names["v"], (self.n_kv * self.dv, self.hidden)),
+                 WeightSpec(self.names["o"], (self.hidden, self.n_q * self.dv))]
         if self.qk_norm:
-            specs += [WeightSpec(self.q_norm_name, (self.d,), role="norm", std=0.1),
-                      WeightSpec(self.k_norm_name, (self.d,), role="norm", std=0.1)]
+            nq, nk = (self.n_q * self.d, self.n_kv * self.d) if self.norm_whole else (self.d, self.d)
+            specs += [WeightSpec(self.q_norm_name, (nq,), role="norm", std=0.1),
+                      WeightSpec(self.k_norm_name, (nk,), role="norm", std=0.1)]
+        if self.weights == "sigmoid":
+            specs.append(WeightSpec(self.bias_name, (self.n_q,), role="vector", std=0.5))
         return specs
 
     def load(self, tensors):
@@ -74,18 +109,20 @@ class Attention(Mixer):
             # fp32 copies for the decode kernel that does the norm itself
             self.q_norm_f32 = self.q_norm_w.float().contiguous()
             self.k_norm_f32 = self.k_norm_w.float().contiguous()
+        if self.weights == "sigmoid":
+            self.bias = tensors[self.bias_name].float().contiguous()
 
     def weight_bytes(self):
-        return (self.qkv_cols * self.hidden + self.hidden * self.n_q * self.d) * self.rt.dtype.itemsize
+        return (self.qkv_cols * self.hidden + self.hidden * self.n_q * self.dv) * self.rt.dtype.itemsize
 
     def scratch_bytes(self, max_tokens):
-        return max_tokens * (self.qkv_cols + self.n_q * self.d) * self.rt.dtype.itemsize
+        return max_tokens * (self.qkv_cols + self.n_q * self.dv) * self.rt.dtype.itemsize
 
     def load_transient_bytes(self):
         return self.qkv_cols * self.hidden * self.rt.dtype.itemsize       # q, k, v beside their stacked copy
 
     def cache_request(self):
-        return PagedKV(self.n_kv, self.d, self.window)
+        return PagedKV(self.n_kv, self.d, self.window, value_head_dim=self.dv)
 
     def _out_proj(self, attn, hidden, then):
         """``hidden += W_o attn``; folds the norm that follows (``then``) into the product if it can."""
@@ -109,6 +146,9 @@ class Attention(Mixer):
                 rt.ops.linear(x.materialize(), self.w_qkv, qkv)
         else:
             rt.ops.linear(x, self.w_qkv, qkv)
+        if self.general:
+            self._forward_general(ctx, cache, qkv, hidden, then)
+            return
         table, rotary_dim, pairing = None, 0, None
         if self.pos is not None:
             table = self.pos.rotary_table()
@@ -145,4 +185,27 @@ class Attention(Mixer):
                                       cache if cache.writes else None, **extra)
         rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale,
                          self.window, cache)
+        self._out_proj(attn, hidden, then)
+
+    def _forward_general(self, ctx, cache, qkv, hidden, then):
+        """Masks, weight rules, norms and widths beyond the reference's layer: one kernel norms and
+        rotates q and k in fp32 and writes the new keys and values into their pages, one does the
+        attention over the pages.  A layer that is causal softmax attention with equal key and
+        value widths goes on to the framework's tuned attention kernels from there."""
+        rt, ops = self.rt, self.rt.ops
+        n = hidden.shape[0]
+        freqs, pairing = (None, "half_split") if self.pos is None else (self.pos.frequencies(), self.pos.pairing)
+        if self.pos is not None and getattr(self.pos, "magnitude", 1.0) != 1.0:
+            raise ValueError("attention: a scaled rotation is not among this kernel's forms")
+        ops.attention_prepare(ctx, qkv, self.n_q, self.n_kv, self.d, self.dv,
+                              "whole" if self.norm_whole else ("per_head" if self.qk_norm else None),
+                              self.q_norm_f32 if self.qk_norm else None, self.k_norm_f32 if self.qk_norm else None,
+                              self.eps, freqs, pairing, cache if cache.writes else None)
+        attn = rt.buffer("attn_out", n, self.n_q * self.dv, rt.dtype)
+        if self.weights == "softmax" and self.mask != "chunk" and self.dv == self.d:
+            ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale, self.window, cache)
+        else:
+            size = self.window if self.mask == "window" else (self.chunk if self.mask == "chunk" else 0)
+            ops.attention_masked(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.dv, self.scale, self.mask,
+                                 int(size or 0), self.weights, self.bias, cache)
         self._out_proj(attn, hidden, then)

@@ -37,6 +37,10 @@ Interfaces, by kind:
     norm (normed wanted rows → fp32 logits).  A multiplier, learned positions added to the
     token rows, a logit scale or soft cap live in parts of these two kinds.
 
+``Injection.forward(ctx, hidden, origin) -> None``
+    A part that stands between two layers and rewrites the stream from the stream and from what
+    the embedding left (``origin``), for models that feed the embedding in again.
+
 A mixer whose ``__init__`` takes a ``position_encodings`` keyword is given the model's named
 position encodings (a dict) when it is built; one without it is built from ``(params, rt)``.
 """
@@ -308,6 +312,23 @@ class Head(Part):
 
     def weight_bytes(self) -> int:
         """Bytes of weights one step reads here."""
+        return 0
+
+
+class Injection(Part):
+    """Rewrites the residual stream between two layers.  Its tensors are named in full (no layer
+    prefix).  ``params`` always hold ``hidden_size``."""
+
+    def begin_step(self, ctx) -> None:
+        """Called once per forward pass before any layer runs (a part that runs at several
+        places of a step may share work between them)."""
+
+    def forward(self, ctx, hidden, origin) -> None:
+        """``hidden``: the fp32 residual stream, rewritten in place; ``origin``: what the embedding
+        left for the step's tokens (fp32, same shape, read only)."""
+        raise NotImplementedError
+
+    def weight_bytes(self) -> int:
         return 0
 
 

@@ -7,13 +7,15 @@ from .base import Block
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
-    """``h += mixer(norm(h)); h += ffn(norm(h))`` (crates/leone/src/runtime.rs:9103-9317)."""
+    """``h += mixer(norm(h)); h += ffn(norm(h))`` (crates/leone/src/runtime.rs:9103-9317).  A layer
+    without a feed-forward (and without its norm) is the first half only."""
 
     chains_norms = True       # forward takes pre= and after= (see below)
 
     def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, **extra):
-        if feed_forward is None or mixer_norm is None or ffn_norm is None or extra:
-            raise ValueError("the pre_norm arrangement is norm, mixer, norm, feed-forward: it takes exactly those parts")
+        if mixer_norm is None or (feed_forward is None) != (ffn_norm is None) or extra:
+            raise ValueError("the pre_norm arrangement is norm, mixer and, optionally, norm, feed-forward: "
+                             "it takes exactly those parts")
         super().__init__(mixer, feed_forward, mixer_norm, ffn_norm)
 
     def entry_norm(self, ctx, hidden):
@@ -28,6 +30,12 @@ class PreNormBlock(Block):
         product (or None); ``after``: the next block's entry norm for this block's last product
         to fold in.  Returns ``after`` if it was filled, else None."""
         x = pre if pre is not None and pre.ready else self.mixer_norm.forward(ctx, hidden)
+        if self.feed_forward is None:
+            if after is not None and getattr(self.mixer, "fuses_following_norm", False):
+                self.mixer.forward(ctx, cache, x, hidden, then=after)
+            else:
+                self.mixer.forward(ctx, cache, x, hidden)
+            return after if after is not None and after.ready else None
         mid = None
         if getattr(self.mixer, "fuses_following_norm", False) and \
                 getattr(self.feed_forward, "accepts_deferred_norm", False):

@@ -7,6 +7,13 @@ multiplies the expert's input (``scale = "input"``: ``sum expert_e(w_e x)``) or 
 (``"output"``).  An expert is ``W_down (silu(W_gate a) * (W_up a))`` without biases.  An optional
 shared expert of the same form (size ``shared_size``) runs on every token and is added.
 
+Further parameters, each off by default: ``expert_form = "relu_squared"`` makes an expert the
+ungated ``W_down max(W_up a, 0)^2`` (tensors ``up`` and ``down`` only); ``groups`` and
+``groups_kept`` restrict the choice to the experts of the best groups (the experts form ``groups``
+equal runs of neighbours, a run is worth its largest score, the ``groups_kept`` best runs stay, the
+lowest index among equal ones); ``weight_scale`` multiplies the chosen weights (after an optional
+renormalisation).
+
 Experts' matrices are stacked at load time (``[experts, ff, hidden]`` twice and ``[experts, hidden,
 ff]``); the pairs (token, choice) are grouped by expert on the device and the grouped products run
 over them, so nothing is read back by the host and a captured decode step can replay it.
@@ -32,8 +39,20 @@ class RoutedExperts(FeedForward):
         self.scale = params.get("scale", "input")
         shared = params.get("shared_size")
         self.shared_ff = int(shared) if shared else None
+        self.form = params.get("expert_form", "gated_silu")
+        self.groups = int(params.get("groups", 1))
+        self.groups_kept = int(params.get("groups_kept", self.groups))
+        self.weight_scale = float(params.get("weight_scale", 1.0))
         if self.score not in ("sigmoid", "softmax") or self.scale not in ("input", "output"):
             raise ValueError(f"routed experts: score '{self.score}' / scale '{self.scale}'")
+        if self.form not in ("gated_silu", "relu_squared"):
+            raise ValueError(f"routed experts: expert form '{self.form}'")
+        if self.groups < 1 or self.experts % self.groups or not 0 < self.groups_kept <= self.groups or \
+                self.top > self.experts // self.groups * self.groups_kept:
+            raise ValueError(f"routed experts: {self.experts} experts in {self.groups} groups, {self.groups_kept} kept, "
+                             f"{self.top} chosen")
+        if self.form == "relu_squared" and self.scale == "input":
+            raise ValueError("routed experts: ungated experts are weighted at their output")
         if not 0 < self.top <= self.experts:
             raise ValueError(f"routed experts: top {self.top} of {self.experts}")
         self.router_name = params.get("router_name", "router")
@@ -44,11 +63,16 @@ class RoutedExperts(FeedForward):
     def _expert(self, e, which):
         return self.expert_pattern.format(e, which)
 
+    @property
+    def gated(self):
+        return self.form == "gated_silu"
+
     def weight_specs(self):
         specs = []
         for e in range(self.experts):
-            specs += [WeightSpec(self._expert(e, "gate"), (self.ff, self.hidden)),
-                      WeightSpec(self._expert(e, "up"), (self.ff, self.hidden)),
+            if self.gated:
+                specs.append(WeightSpec(self._expert(e, "gate"), (self.ff, self.hidden)))
+            specs += [WeightSpec(self._expert(e, "up"), (self.ff, self.hidden)),
                       WeightSpec(self._expert(e, "down"), (self.hidden, self.ff))]
         specs.append(WeightSpec(self.router_name, (self.experts, self.hidden)))
         if self.shared_ff:
@@ -60,7 +84,7 @@ class RoutedExperts(FeedForward):
     def load(self, tensors):
         def stack(which):
             return torch.stack([tensors[self._expert(e, which)] for e in range(self.experts)]).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.w_gate, self.w_up, self.w_down = stack("gate") if self.gated else None, stack("up"), stack("down")
         self.w_router = self.rt.ops.prepare_matrix(tensors[self.router_name].contiguous())
         if self.shared_ff:
             ops = self.rt.ops
@@ -70,7 +94,7 @@ class RoutedExperts(FeedForward):
 
     def weight_bytes(self):
         # a decode step reads the router, the shared expert and `top` experts per token (at most all)
-        per_expert = 3 * self.ff * self.hidden
+        per_expert = (3 if self.gated else 2) * self.ff * self.hidden
         return (self.experts * self.hidden + 3 * (self.shared_ff or 0) * self.hidden
                 + self.top * per_expert) * self.rt.dtype.itemsize
 
@@ -81,7 +105,7 @@ class RoutedExperts(FeedForward):
             + max_tokens * 3 * (self.shared_ff or 0) * item
 
     def load_transient_bytes(self):
-        return 3 * self.experts * self.ff * self.hidden * self.rt.dtype.itemsize
+        return (3 if self.gated else 2) * self.experts * self.ff * self.hidden * self.rt.dtype.itemsize
 
     def forward(self, ctx, x, hidden):
         rt, ops = self.rt, self.rt.ops
@@ -89,7 +113,10 @@ class RoutedExperts(FeedForward):
         pairs = n * self.top
         chosen = rt.flat_buffer("experts_chosen", pairs, torch.int32, reserve=rt.max_tokens * self.top)[:pairs]
         weight = rt.flat_buffer("experts_weight", pairs, torch.float32, reserve=rt.max_tokens * self.top)[:pairs]
-        ops.experts_route(x, self.w_router, chosen, weight, self.top, self.score == "softmax", self.renormalize)
+        extra = {}
+        if self.groups > 1 or self.weight_scale != 1.0:
+            extra = dict(groups=self.groups, groups_kept=self.groups_kept, weight_scale=self.weight_scale)
+        ops.experts_route(x, self.w_router, chosen, weight, self.top, self.score == "softmax", self.renormalize, **extra)
         ops.experts_forward(x, self.w_gate, self.w_up, self.w_down, chosen, weight, self.top,
                             self.scale == "input", hidden, rt)
         if self.shared_ff:

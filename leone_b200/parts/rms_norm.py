@@ -3,7 +3,9 @@
 ``y_c = x_c * w_c / sqrt(mean_c(x_c^2) + eps)`` with the sum of squares in
 fp32; the weight multiplies directly, not as ``1 + w``
 (crates/leone/src/cpu.rs:1642-1663; CUDA counterpart
-crates/leone-cuda/cuda/ie_cuda.cu:2357-2380).
+crates/leone-cuda/cuda/ie_cuda.cu:2357-2380).  ``weight_offset`` (default 0) is this part's own
+parameter for models that store the gain as its distance from a constant: the gain is
+``weight_offset + w``, formed once at load time in fp32.
 """
 from __future__ import annotations
 
@@ -18,13 +20,17 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.name = params.get("name", "weight")
+        self.offset = float(params.get("weight_offset", 0.0))
         self.weight = self.weight_f32 = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name, (self.size,), role="norm", std=0.1)]
+        # a gain stored around zero is drawn around zero
+        return [WeightSpec(self.name, (self.size,), role="vector" if self.offset else "norm", std=0.1)]
 
     def load(self, tensors):
         self.weight = tensors[self.name]
+        if self.offset:
+            self.weight = (self.weight.float() + self.offset).contiguous()
         self.weight_f32 = self.weight.float().contiguous()    # for a product that applies the norm itself
 
     def defer(self, ctx, hidden, tag="a"):

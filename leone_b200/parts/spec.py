@@ -64,6 +64,10 @@ class ModelSpec:
     # engine adds ``vocab_size`` and ``hidden_size`` to the params of either.
     embedding: Optional[PartSpec] = None
     head: Optional[PartSpec] = None
+    # Parts that rewrite the residual stream between layers: ``(run position, spec)`` pairs; the part
+    # (registry ``INJECTIONS``) runs right before the layer at that position of the run order and
+    # sees the stream and what the embedding left.  Equal specs are one part (shared weights).
+    injections: Tuple[Tuple[int, PartSpec], ...] = ()
 
     def embedding_spec(self) -> PartSpec:
         base = self.embedding or PartSpec("token_embedding", {"name": self.embedding_name})
@@ -85,6 +89,9 @@ class ModelSpec:
         for idx in self.run_order:
             if not 0 <= idx < n:
                 raise ValueError(f"run_order names layer {idx}, but there are {n} layers")
+        for pos, _ in self.injections:
+            if not 0 <= pos < len(self.run_order):
+                raise ValueError(f"an injection names run position {pos}, but {len(self.run_order)} layers run")
         first_run = {}
         for step, idx in enumerate(self.run_order):
             first_run.setdefault(idx, step)

@@ -50,13 +50,70 @@ class EmulatedOps:
             y = y + residual
         out.copy_(y.to(out.dtype))
 
-    def linear_swiglu(self, x, w_gate_up, out):
+    def linear_swiglu(self, x, w_gate_up, out, gate_shape=None):
         y = x.float() @ w_gate_up.float().t()
         inter = y.shape[1] // 2
         if self.dtype != torch.float32:
             y = y.to(self.dtype).float()
         g, u = y[:, :inter], y[:, inter:]
-        out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+        slope, limit, shift = gate_shape or (1.0, float("inf"), 0.0)
+        g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+        out.copy_((g / (1.0 + torch.exp(-slope * g)) * (u + shift)).to(out.dtype))
+
+    def convert(self, src, out):
+        out.copy_(src.to(out.dtype))
+
+    def attention_prepare(self, ctx, qkv, n_q, n_kv, dk, dv, norm, q_w, k_w, eps, freqs, pairing, cache):
+        n = qkv.shape[0]
+        x = qkv.float()
+        q, k = x[:, :n_q * dk], x[:, n_q * dk:(n_q + n_kv) * dk]
+        v = qkv[:, (n_q + n_kv) * dk:]
+        if norm == "whole":
+            q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps) * q_w.float()
+            k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps) * k_w.float()
+        q, k = q.reshape(n, n_q, dk), k.reshape(n, n_kv, dk)
+        if norm == "per_head":
+            q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps) * q_w.float()
+            k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps) * k_w.float()
+        pos = ctx.positions.long()
+        q = self._rotate(q, pos, freqs, 1.0, pairing).to(qkv.dtype)
+        k = self._rotate(k, pos, freqs, 1.0, pairing).to(qkv.dtype)
+        qkv[:, :n_q * dk] = q.reshape(n, -1)
+        qkv[:, n_q * dk:(n_q + n_kv) * dk] = k.reshape(n, -1)
+        if cache is None:
+            return
+        pt = cache.page_tokens
+        page = cache.block_table[ctx.seq_of_token.long(), pos // pt].long()
+        assert (page >= 0).all(), "write into a block without a page"
+        cache.k_pool[page, :, pos % pt, :] = k
+        cache.v_pool[page, :, pos % pt, :] = v.reshape(n, n_kv, dv)
+
+    def attention_masked(self, ctx, qkv, out, n_q, n_kv, dk, dv, scale, mask, mask_size, weights, bias, cache):
+        n = qkv.shape[0]
+        q = qkv.float()[:, :n_q * dk].view(n, n_q, dk)
+        g = n_q // n_kv
+        pt = cache.page_tokens
+        res = torch.zeros(n, n_q, dv)
+        positions, seqs = ctx.positions.tolist(), ctx.seq_of_token.tolist()
+        for t in range(n):
+            p, s = positions[t], seqs[t]
+            lo = {"causal": 0, "window": max(0, p - mask_size + 1) if mask_size else 0,
+                  "chunk": (p // mask_size) * mask_size if mask_size else 0}[mask]
+            idx = torch.arange(lo, p + 1)
+            pages = cache.block_table[s, idx // pt].long()
+            assert (pages >= 0).all(), "read from a block without a page"
+            keys = cache.k_pool[pages, :, idx % pt, :].float()      # [ctx, n_kv, dk]
+            vals = cache.v_pool[pages, :, idx % pt, :].float()
+            for h in range(n_q):
+                sc = (keys[:, h // g, :] @ q[t, h]) * scale
+                if weights == "sigmoid":
+                    w = torch.sigmoid(sc + bias[h])
+                elif weights == "softmax_plus_one":
+                    w = torch.softmax(torch.cat([sc, torch.zeros(1)]), dim=0)[:-1]
+                else:
+                    w = torch.softmax(sc, dim=0)
+                res[t, h] = (w[:, None] * vals[:, h // g, :]).sum(0)
+        out.copy_(res.reshape(n, n_q * dv).to(out.dtype))
 
     def qk_norm_rope_write(self, ctx, qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, table,
                            rotary_dim, cache, pairing="half_split"):
@@ -215,14 +272,19 @@ class EmulatedOps:
                 res[t] *= torch.sigmoid(gate[t, :heads].float())[:, None]
         out.copy_(res.reshape(n, heads * dv).to(out.dtype))
 
-    def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False):
+    def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False, groups=1,
+                      groups_kept=None, weight_scale=1.0):
         z = x.float() @ w_router.float().t()
         s = torch.softmax(z, dim=-1) if softmax else torch.sigmoid(z)
+        if groups > 1 and (groups_kept or groups) < groups:
+            worth = s.view(s.shape[0], groups, -1).max(dim=-1).values
+            kept = torch.zeros_like(worth, dtype=torch.bool).scatter_(1, torch.topk(worth, groups_kept, dim=-1).indices, True)
+            s = s.masked_fill(~kept.repeat_interleave(s.shape[1] // groups, dim=1), float("-inf"))
         val, idx = torch.topk(s, top, dim=-1)
         if renormalize:
             val = val / val.sum(dim=-1, keepdim=True)
         chosen.copy_(idx.reshape(-1).to(torch.int32))
-        weight.copy_(val.reshape(-1))
+        weight.copy_(val.reshape(-1) * weight_scale)
 
     def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
         n = x.shape[0]
@@ -232,7 +294,10 @@ class EmulatedOps:
             for j in range(top):
                 e, w = int(chosen[t * top + j]), weight[t * top + j]
                 a = xf[t] * w if scale_input else xf[t]
-                y = w_down[e].float() @ (silu(w_gate[e].float() @ a) * (w_up[e].float() @ a))
+                if w_gate is None:
+                    y = w_down[e].float() @ (torch.relu(w_up[e].float() @ a) ** 2)
+                else:
+                    y = w_down[e].float() @ (silu(w_gate[e].float() @ a) * (w_up[e].float() @ a))
                 hidden[t] += y if scale_input else y * w
 
     def sample(self, logits, temperature, seeds, positions, out):
