@@ -35,7 +35,7 @@ MODULES: Dict[str, List[str]] = {
     # linear attention with a decaying state, attention through a cached latent, attention with a choice
     # of mask and weight rule, routed experts
     "mixers": ["linear_attention.cu", "attention_latent.cu", "attention_latent_mma.cu", "attention_masked.cu",
-               "experts.cu", "norm_act.cu"],
+               "attention_masked_mma.cu", "experts.cu", "norm_act.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
     # the host side of the runtime (pages, block tables, step metadata, the scheduler's decisions,

@@ -204,7 +204,9 @@ class CudaOps:
         ``d.xn = bf16(out * d.weight)`` and the sums of ``out^2`` in ``d.ss``) or as the one
         after it (``linear(d.xn, ..., norm_in=d)`` scales its rows by the norm's factor)."""
         wt = w.weight
+        # (a gate/up pair takes part only in the interleaved layout of the fused gated epilogue)
         return (self.fast is not None and self.fast.fuses_norm(n_tokens, wt.shape[0], wt.shape[1])
+                and getattr(w, "gate_up_layout", "interleaved16") == "interleaved16"
                 and wt.dtype == torch.bfloat16
                 and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0 and wt.stride(0) % 8 == 0
                 and wt.data_ptr() % 16 == 0)
@@ -445,8 +447,34 @@ class CudaOps:
             bt.shape[0], _ptr(ctx.status), self._stream()), "attention_masked")
 
     def attention_masked_tiled(self, ctx, qkv, out, n_q, n_kv, dk, dv, scale, mask, mask_size, weights, bias, cache) -> bool:
-        """The tensor-core form of :meth:`attention_masked` where there is one for these sizes."""
-        return False
+        """The tensor-core form of :meth:`attention_masked` (``csrc/attention_masked_mma.cu``) where
+        there is one for these sizes: bfloat16, key and value widths multiples of 16 up to 128, up
+        to 64 query heads per KV head (16 in a decode step, whose keys are also split over blocks
+        until the SMs are busy)."""
+        decode = bool(ctx.decode_only)
+        if (qkv.dtype != torch.bfloat16 or os.environ.get("LEONE_NO_MASKED_MMA", "0") == "1"
+                or getattr(ctx, "q_start", None) is None
+                or not self.mixers.leone_attention_masked_mma_supported(n_q, n_kv, dk, dv, 1 if decode else 0)
+                or qkv.stride(0) % 8 or out.stride(0) % 2):
+            return False
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        splits, partial = 1, None
+        if decode:
+            keys = min(int(mask_size), ctx.max_ctx_len) if mask != "causal" else ctx.max_ctx_len
+            tiles = -(-keys // 64) + 1
+            splits = max(1, min(64, tiles // 4, (2 * 148) // max(ctx.n_seqs * n_kv, 1)))
+            if splits > 1:
+                self.mixers.leone_attention_masked_mma_scratch.restype = ctypes.c_longlong
+                need = int(self.mixers.leone_attention_masked_mma_scratch(ctx.n_seqs, n_kv, dv, splits))
+                partial = self._scratch("masked_partial", -(-need // 64), 64, torch.float32)
+                self.launches += 1
+        _check(self.mixers.leone_attention_masked_mma(
+            _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt), bt.shape[1],
+            _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs, 1 if decode else int(ctx.max_q_len), n_q, n_kv, dk, dv,
+            c_float(scale), self._MASKS[mask], int(mask_size), self._WEIGHTS[weights], _ptr(bias), cache.page_tokens,
+            kp.shape[0], 1 if decode else 0, splits, _ptr(partial), _ptr(ctx.status), self._stream()),
+            "attention_masked_mma")
+        return True
 
     # -- mixers and feed-forwards of the 'mixers' module (compiled when a model first needs it) ----
     @property
