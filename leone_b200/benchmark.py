@@ -391,6 +391,36 @@ def _sarizen_shape(width: int, layers: int, heads: int, experts: int, top: int, 
             "layers": out}
 
 
+def _malapel_shape(width: int, runs: int, heads: int, experts: int, top: int, expert_ff: int, window: int,
+                   chunk: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: the three mixers in turn (sliding window, chunks, causal,
+    causal), dense feed-forwards alternating with routed experts of the same active size, four query
+    heads to a key/value head; the first two layers run twice, so ``runs`` layer runs need ``runs - 2``
+    layers."""
+    def mix(kind, size=None):
+        m = {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+             "rot": {"base": 1000000.0, "dims": 128}}
+        if size:
+            m["mask"] = {"size": size}
+        return kind, m
+    kinds = [mix("attention_3", window), mix("attention", chunk), mix("attention_2"), mix("attention_2")]
+    dense = {"kind": "dense", "ff": top * expert_ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 8, "keep": 4}}}
+    out = []
+    for i in range(runs - 2):
+        kind, m = kinds[i % 4]
+        out.append({"type": kind, "mixer": m, "mlp": dense if i % 2 == 0 else moe})
+    return {"architecture": "Malapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "loop": {"start": 0, "stop": 2, "times": 2}, "layers": out}
+
+
+MALAPEL_SIZES = {
+    # name: (width, layer runs, heads, experts, top, expert ff, window, chunk, vocab)
+    "small": (2048, 8, 16, 32, 4, 768, 1024, 1024, 32768),
+    "medium": (4096, 8, 32, 64, 8, 1024, 2048, 2048, 65536),
+}
+
 DESIGN_SIZES = {
     # name: (width, layers, heads, experts, top, expert ff, shared ff, kv rank, window, vocab)
     "small": (2048, 8, 16, 32, 4, 512, 1024, 512, 1024, 32768),
@@ -409,7 +439,8 @@ class _OpTimer:
     def __enter__(self):
         names = ["linear", "linear_swiglu", "rms_norm", "rms_norm_pair", "relu_squared", "linear_per_head",
                  "linear_attention", "gate_norm", "latent_prepare", "attention_latent", "experts_route",
-                 "experts_forward", "attention", "qk_norm_rope_write", "embedding", "logit_post"]
+                 "experts_forward", "attention", "qk_norm_rope_write", "embedding", "logit_post", "attention_prepare",
+                 "attention_masked", "convert"]
         for name in names:
             fn = getattr(self.ops, name, None)
             if fn is None:
@@ -480,10 +511,15 @@ def compare_designs(design: str = "sarizen", size: str = "small", steps: int = 6
     call in one prompt step and one decode step of each.  Prints one JSON line."""
     from .engine.engine import Engine
     from .registry import config_from_dict
-    if design != "sarizen":
+    if design == "malapel":
+        width, layers, heads, experts, top, expert_ff, window, chunk, vocab = MALAPEL_SIZES[size]
+        raw = _malapel_shape(width, layers, heads, experts, top, expert_ff, window, chunk, vocab)
+        shared_ff, rank = 0, 0
+    elif design == "sarizen":
+        width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab = DESIGN_SIZES[size]
+        raw = _sarizen_shape(width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab)
+    else:
         raise ValueError(f"unknown design '{design}'")
-    width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab = DESIGN_SIZES[size]
-    raw = _sarizen_shape(width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab)
     dense = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=width,
                  num_attention_heads=heads, num_key_value_heads=max(heads // 4, 1), head_dim=128,
                  intermediate_size=top * expert_ff + shared_ff, vocab_size=vocab, rope_theta=1000000.0,

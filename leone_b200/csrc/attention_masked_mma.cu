@@ -33,6 +33,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// 2^x by the special-function unit (2^-inf = 0); scores are kept in units of log 2 so that a weight
+// costs one subtraction and one of these.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
 __device__ __forceinline__ int mm_first_seen(int mask, int size, int pos) {
   if (mask == 1) return max(0, pos - size + 1);
   if (mask == 2) return (pos / size) * size;
@@ -66,8 +74,10 @@ __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int k
                                              uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int me, int lanes,
                                              int tok_row) {
   const int kc = a.dk >> 3, vc = a.dv >> 3;         // 16-byte chunks per row
-  for (int c = me; c < kMmKeys * (kc + vc); c += lanes) {
-    const int r = c / (kc + vc), w = c - r * (kc + vc);
+  // a block's threads pair up on a key row, a warp's lanes take whole rows: one look-up of the
+  // row's page per thread, then copies that depend on nothing else
+  const int tpr = lanes >= 128 ? 2 : 1, sub = me % tpr;
+  for (int r = me / tpr; r < kMmKeys; r += lanes / tpr) {
     const int j = j0 + r;
     bool ok = j >= lo && j <= hi;
     long long slot = 0;
@@ -78,24 +88,26 @@ __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int k
         set_status(a.status, kBadPage, tok_row, page, j);
         ok = false;
       } else {
-        slot = ((long long)page * a.n_kv + kvh) * a.page_tokens + (j % a.page_tokens);
+        slot = ((long long)page * a.n_kv + kvh) * a.page_tokens + (j - blk * a.page_tokens);
       }
     }
-    if (w < kc)
-      cp_async16_zfill(k_s + (r * pitch_k + w * 8) * 2, ok ? (const void*)(a.k_pool + slot * a.dk + w * 8) : (const void*)a.k_pool, ok);
-    else
-      cp_async16_zfill(v_s + (r * pitch_v + (w - kc) * 8) * 2,
-                       ok ? (const void*)(a.v_pool + slot * a.dv + (w - kc) * 8) : (const void*)a.v_pool, ok);
+    const __nv_bfloat16* ks = a.k_pool + slot * a.dk;
+    const __nv_bfloat16* vs = a.v_pool + slot * a.dv;
+    const uint32_t kd = k_s + r * pitch_k * 2, vd = v_s + r * pitch_v * 2;
+    for (int w = sub; w < kc; w += tpr) cp_async16_zfill(kd + w * 16, ok ? (const void*)(ks + w * 8) : (const void*)a.k_pool, ok);
+    for (int w = sub; w < vc; w += tpr) cp_async16_zfill(vd + w * 16, ok ? (const void*)(vs + w * 8) : (const void*)a.v_pool, ok);
   }
 }
 
 // One warp, 16 rows, one tile of 64 keys: scores, weights, and the sums into o.  Row `g` (and g + 8)
-// of the warp sees keys [lo_r, hi_r] (absolute positions); the tile starts at key j0.
+// of the warp sees keys [lo_r, hi_r] (absolute positions); the tile starts at key j0.  `full`
+// (uniform in the warp): every row sees every key of the tile, so no key is tested.  `scale2` is
+// the score scale times log2(e), the bias and the running maximum are in the same units.
 template <int DKT, int DVT>
 __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int dkt,
-                                          int dvt, int lane, int j0, const int (&lo_r)[2], const int (&hi_r)[2],
-                                          float scale, int weights, const float (&bias_r)[2], float (&m_run)[2],
-                                          float (&l_run)[2], float (&o)[2 * DVT][4]) {
+                                          int dvt, int lane, int j0, bool full, const int (&lo_r)[2],
+                                          const int (&hi_r)[2], float scale2, int weights, const float (&bias_r)[2],
+                                          float (&m_run)[2], float (&l_run)[2], float (&o)[2 * DVT][4]) {
   float s[8][4];
 #pragma unroll
   for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -115,26 +127,31 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
     }
   }
   const int tq = lane & 3;
-  // scores -> weights; element i of n-tile n: row half i >> 1, key j0 + n * 8 + 2 * tq + (i & 1)
-  if (weights == 2) {
+  // scores -> weights; element i of n-tile n: row half i >> 1, key j0 + n * 8 + 2 * tq + (i & 1).
+  // Keys a row does not see get the score -inf (scale2 > 0 keeps it), which every rule turns into 0.
+  if (!full) {
 #pragma unroll
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int h = i >> 1, j = j0 + n * 8 + 2 * tq + (i & 1);
-        const bool ok = j >= lo_r[h] && j <= hi_r[h];
-        s[n][i] = ok ? __fdividef(1.f, 1.f + __expf(-(s[n][i] * scale + bias_r[h]))) : 0.f;
+        if (j < lo_r[h] || j > hi_r[h]) s[n][i] = -INFINITY;
       }
+  }
+  if (weights == 2) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)      // the reciprocal of 1 + 2^+inf is 0
+        s[n][i] = __frcp_rn(1.f + fast_exp2(-fmaf(s[n][i], scale2, bias_r[i >> 1])));
   } else {
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int h = i >> 1, j = j0 + n * 8 + 2 * tq + (i & 1);
-        const bool ok = j >= lo_r[h] && j <= hi_r[h];
-        s[n][i] = ok ? s[n][i] * scale : -INFINITY;
-        tile_max[h] = fmaxf(tile_max[h], s[n][i]);
+        s[n][i] *= scale2;
+        tile_max[i >> 1] = fmaxf(tile_max[i >> 1], s[n][i]);
       }
     float alpha[2], m_use[2];
 #pragma unroll
@@ -143,7 +160,7 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
       tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
       const float m_new = fmaxf(m_run[h], tile_max[h]);
       m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[h] = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - m_use[h]);
+      alpha[h] = m_run[h] == -INFINITY ? 0.f : fast_exp2(m_run[h] - m_use[h]);
       m_run[h] = m_new;
       l_run[h] *= alpha[h];
     }
@@ -158,7 +175,7 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float p = __expf(s[n][i] - m_use[i >> 1]);      // exp(-inf) = 0 for keys the row does not see
+        const float p = fast_exp2(s[n][i] - m_use[i >> 1]);      // 2^-inf = 0 for keys the row does not see
         s[n][i] = p;
         l_run[i >> 1] += p;
       }
@@ -234,8 +251,13 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
     const int pos = start + tok0 + tl;
     hi_r[h] = ok ? pos : -1;
     lo_r[h] = ok ? mm_first_seen(a.mask, a.mask_size, pos) : 0;
-    bias_r[h] = (a.weights == 2 && ok) ? a.bias[kvh * g + hg] : 0.f;
+    bias_r[h] = (a.weights == 2 && ok) ? a.bias[kvh * g + hg] * kLog2e : 0.f;
   }
+  // the warp's rows: the tokens they belong to, for tiles that every row sees in full
+  const int w_tok_first = (warp * 16) / g, w_tok_last = min((warp * 16 + 15) / g, n_tok - 1);
+  const bool w_all_valid = (warp * 16 + 15) / g < n_tok;
+  const int w_lo_max = mm_first_seen(a.mask, a.mask_size, start + tok0 + max(w_tok_last, 0));
+  const int w_hi_min = start + tok0 + w_tok_first;
   float m_run[2], l_run[2];
   // the silent member: maximum 0 and, in one of the four lanes that share a row, denominator 1
   m_run[0] = m_run[1] = a.weights == 1 ? 0.f : -INFINITY;
@@ -258,9 +280,10 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
     const int w_first_tok = (warp * 16) / g;
     const bool any = w_first_tok < n_tok && j0 <= w_hi &&
                      j0 + kMmKeys - 1 >= mm_first_seen(a.mask, a.mask_size, start + tok0 + w_first_tok);
+    const bool full = w_all_valid && j0 >= w_lo_max && j0 + kMmKeys - 1 <= w_hi_min;
     if (any)
       tile_step<DKT, DVT>(q_s + warp * 16 * pitch_k * 2, cur, cur + kMmKeys * pitch_k * 2, pitch_k, pitch_v, dkt, dvt, lane,
-                          j0, lo_r, hi_r, a.scale, a.weights, bias_r, m_run, l_run, o);
+                          j0, full, lo_r, hi_r, a.scale * kLog2e, a.weights, bias_r, m_run, l_run, o);
     __syncthreads();
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -327,7 +350,7 @@ attention_masked_decode_kernel(const MaskedArgs a) {
     const int r = gq + 8 * h;
     hi_r[h] = r < g ? pos : -1;
     lo_r[h] = k_lo;
-    bias_r[h] = (a.weights == 2 && r < g) ? a.bias[kvh * g + r] : 0.f;
+    bias_r[h] = (a.weights == 2 && r < g) ? a.bias[kvh * g + r] * kLog2e : 0.f;
   }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[2 * DVT][4];
@@ -339,8 +362,8 @@ attention_masked_decode_kernel(const MaskedArgs a) {
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
-    tile_step<DKT, DVT>(q_s, my_k, my_v, pitch_k, pitch_v, dkt, dvt, lane, j0, lo_r, hi_r, a.scale, a.weights, bias_r,
-                        m_run, l_run, o);
+    tile_step<DKT, DVT>(q_s, my_k, my_v, pitch_k, pitch_v, dkt, dvt, lane, j0, false, lo_r, hi_r, a.scale * kLog2e,
+                        a.weights, bias_r, m_run, l_run, o);
     __syncwarp();
   }
   // the four warps' partial results into shared memory (over the tiles, which are done with)
@@ -376,10 +399,10 @@ attention_masked_decode_kernel(const MaskedArgs a) {
     float f[4], l = 0.f;
     for (int w = 0; w < 4; ++w) {
       const float mw = part[((size_t)w * 16 + r) * pw + a.dv];
-      f[w] = a.weights == 2 ? 1.f : (mw == -INFINITY ? 0.f : __expf(mw - m));
+      f[w] = a.weights == 2 ? 1.f : (mw == -INFINITY ? 0.f : fast_exp2(mw - m));
       l += f[w] * part[((size_t)w * 16 + r) * pw + a.dv + 1];
     }
-    if (a.weights == 1 && last) l += __expf(-m);
+    if (a.weights == 1 && last) l += fast_exp2(-m);
     if (last) {
       const float inv = a.weights == 2 ? 1.f : (l > 0.f ? 1.f / l : 0.f);
       __nv_bfloat16* dst = a.out + (size_t)row * a.out_stride + (size_t)(kvh * g + r) * a.dv;
@@ -416,10 +439,10 @@ attention_masked_merge_kernel(const MaskedArgs a) {
   float m = a.weights == 1 ? 0.f : -INFINITY;
   if (a.weights != 2)
     for (int s = 0; s < a.splits; ++s) m = fmaxf(m, src[s * step + a.dv]);
-  float l = a.weights == 1 ? __expf(-m) : 0.f;
+  float l = a.weights == 1 ? fast_exp2(-m) : 0.f;      // maxima are in units of log 2
   for (int s = 0; s < a.splits; ++s) {
     const float ms = src[s * step + a.dv];
-    if (a.weights != 2 && ms != -INFINITY) l += __expf(ms - m) * src[s * step + a.dv + 1];
+    if (a.weights != 2 && ms != -INFINITY) l += fast_exp2(ms - m) * src[s * step + a.dv + 1];
   }
   const float inv = a.weights == 2 ? 1.f : (l > 0.f ? 1.f / l : 0.f);
   __nv_bfloat16* dst = a.out + (size_t)a.q_start[seq] * a.out_stride + (size_t)h * a.dv;
@@ -427,7 +450,7 @@ attention_masked_merge_kernel(const MaskedArgs a) {
     float v = 0.f;
     for (int s = 0; s < a.splits; ++s) {
       const float ms = src[s * step + a.dv];
-      const float f = a.weights == 2 ? 1.f : (ms == -INFINITY ? 0.f : __expf(ms - m));
+      const float f = a.weights == 2 ? 1.f : (ms == -INFINITY ? 0.f : fast_exp2(ms - m));
       v += f * src[s * step + c];
     }
     dst[c] = __float2bfloat16_rn(v * inv);

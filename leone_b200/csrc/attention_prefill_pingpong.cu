@@ -109,6 +109,22 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float rcp_fast(float x) {      // 1 / +inf = 0
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// How scores become weights, and what a query sees besides the keys before it.  The reference's
+// layer is {0, 0, null}.  weights 1: softmax with one more member of score 0 that has no value
+// (its share joins the row's sum at the end); weights 2: sigmoid(score + bias[head]) for every
+// seen key on its own, nothing normalised (the running maximum is pinned to 0, so nothing is ever
+// rescaled).  chunk > 0: the query at position p sees only keys from floor(p / chunk) * chunk on.
+struct Rules {
+  int weights;
+  int chunk;
+  const float* bias;
+};
 
 // Byte offset of 16-byte chunk `chunk` (8 elements) of row `row` in a tile of rows of D
 // elements stored as D/64 swizzled halves of [128 rows x 128 bytes].
@@ -174,7 +190,7 @@ __global__ void __launch_bounds__(kBlockThreads)
 attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                                   __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
                                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, int n_q,
-                                  float scale, int window, int* status) {
+                                  float scale, int window, Rules rules, int* status) {
   constexpr int kTileBytes = kKeys * D * 2;             // one K or V tile; a Q tile has the same size
   constexpr int kTmemCols = 512;
   constexpr int kChunks = D / 8;                        // 16-byte chunks per row
@@ -235,6 +251,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
     const int lo1 = min(q_len, tok0 + tq), hi1 = min(q_len, tok0 + 2 * tq);
     int k_lo = 0;
     if (window > 0) k_lo = max(0, start + tok0 - window + 1);
+    if (rules.chunk > 0) k_lo = ((start + tok0) / rules.chunk) * rules.chunk;
     const int tile0 = (k_lo / kKeys) * kKeys;
     const int n0 = (start + hi0 - tile0 + kKeys - 1) / kKeys;
     const int n1 = hi1 > lo1 ? (start + hi1 - tile0 + kKeys - 1) / kKeys : 0;
@@ -367,7 +384,8 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
       const int my_tl = row / g;
       const int my_pos = (my_tl < tq && lo + my_tl < hi) ? start + lo + my_tl : -1;   // -1: row unused
       const int first_pos = start + lo, last_pos = start + hi - 1;
-      const float sl2 = scale * kLog2e;
+      const float my_bias = rules.weights == 2 ? rules.bias[kvh * g + (row - my_tl * g)] * kLog2e : 0.f;
+      const float sl2 = (rules.weights == 2 ? -scale : scale) * kLog2e;      // (see `shift` below)
       const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);      // this warp's lanes
       const uint32_t t_s = t_lane + j * kKeys + half * 64;   // this thread's 64 columns of S_j; P_j over their first 32
       const uint32_t t_o = t_lane + 2 * kKeys + j * kKeys + half * (D / 2);          // its half of the row of O_j
@@ -402,9 +420,11 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         // threads, so the branch is uniform; rows that stand for no token compute on zeros and
         // are never stored).
         const bool all_visible = tile0 + (t + 1) * kKeys - 1 <= first_pos &&
-                                 (window <= 0 || tile0 + t * kKeys > last_pos - window);
+                                 (window <= 0 || tile0 + t * kKeys > last_pos - window) &&
+                                 (rules.chunk <= 0 || tile0 + t * kKeys >= (last_pos / rules.chunk) * rules.chunk);
         // keys first .. first + span (relative to this thread's first key) are visible to this row
-        const int first = window > 0 ? max(my_pos - window + 1 - tile_start, 0) : 0;
+        const int first = window > 0 ? max(my_pos - window + 1 - tile_start, 0)
+                          : (rules.chunk > 0 ? max((max(my_pos, 0) / rules.chunk) * rules.chunk - tile_start, 0) : 0);
         const unsigned span = my_pos >= 0 && my_pos - tile_start >= first ? (unsigned)(my_pos - tile_start - first) : 0u;
         const bool none = my_pos < 0 || my_pos - tile_start < first;      // no key of this thread's columns is visible
         // pass 1: the maximum over the keys the row may see; four running maxima (the chain of
@@ -439,6 +459,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         halves[j][t & 1][half][row] = tile_max;
         named_barrier_sync(bar_id, kTileThreads);        // the two halves of every row's maximum
         tile_max = fmaxf(tile_max, halves[j][t & 1][half ^ 1][row]);
+        if (rules.weights == 2) tile_max = 0.f;          // no maximum is taken out of a sigmoid's argument
         // the running maximum moves only when it must (first key seen) or when the tile's exceeds
         // it by 2^8; both threads of a row decide alike from the same numbers
         float alpha = 1.f;
@@ -467,12 +488,18 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         // then all exponentials, then sums and pairs), so that independent instructions follow
         // each other and the pipes' latencies overlap.
         float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        // the exponent is score * sl - max; for the sigmoid it is -(score * sl + bias), so the scale changes sign
+        const float shift = rules.weights == 2 ? -my_bias : -m_use;
         auto to_p = [&](const uint32_t* r, int c) {
           float x[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) x[i] = fmaf(__uint_as_float(r[i]), sl2, -m_use);
+          for (int i = 0; i < 16; ++i) x[i] = fmaf(__uint_as_float(r[i]), sl2, shift);
 #pragma unroll
           for (int i = 0; i < 16; ++i) x[i] = ex2(x[i]);
+          if (rules.weights == 2) {                      // uniform: 1 / (1 + 2^-(score + bias))
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = rcp_fast(1.f + x[i]);
+          }
           if (!all_visible) {                            // uniform
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = seen(c + i) ? x[i] : 0.f;
@@ -515,10 +542,11 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
       if (nj > 0) {
         halves[j][nj & 1][half][row] = l_run;
         named_barrier_sync(bar_id, kTileThreads);
-        const float l_row = l_run + halves[j][nj & 1][half ^ 1][row];
+        float l_row = l_run + halves[j][nj & 1][half ^ 1][row];
+        if (rules.weights == 1) l_row += ex2(m_run == -INFINITY ? 0.f : -m_run);      // the silent member's share
         if (ok_all && !mbar_wait_long(bar_o + 8 * j, 0, giveup)) ok_all = false;
         tc_fence_after();
-        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+        const float inv = rules.weights == 2 ? 1.f : (l_row > 0.f ? 1.f / l_row : 0.f);
         const bool store = ok_all && my_pos >= 0;
         const int hh = row - my_tl * g;
         __nv_bfloat16* dst = out + (size_t)(q0 + lo + (store ? my_tl : 0)) * out_stride + (size_t)(kvh * g + hh) * D +
@@ -559,7 +587,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
 template <int D>
 int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride, const PagedArgs& pa,
            const int* q_start, const int* ctx_len, int n_seqs, int n_q, int max_q_len, float scale, int window,
-           int* status, cudaStream_t stream) {
+           const Rules& rules, int* status, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_pingpong_kernel<D>,
@@ -571,7 +599,7 @@ int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out
   const int tq = kRows / g;
   dim3 grid(((max_q_len + 2 * tq - 1) / (2 * tq)) * pa.n_kv, 1, n_seqs);
   return launch_kernel(attention_prefill_pingpong_kernel<D>, grid, dim3(kBlockThreads), smem_bytes<D>(), stream,
-                       qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, status);
+                       qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, rules, status);
 }
 
 }  // namespace pingpong
@@ -582,12 +610,18 @@ using namespace leone;
 // Prompt portions and mixed batches on tcgen05, two query tiles per block; arguments as
 // leone_attention_prefill.  Head size 64 or 128, up to 128 query heads per KV head, 16-byte
 // aligned rows.
-extern "C" int leone_attention_prefill_pingpong(const void* qkv, int row_stride, void* out, int out_stride,
-                                                const void* k_pool, const void* v_pool, const int* block_table,
-                                                int table_width, const int* q_start, const int* ctx_len, int n_seqs,
-                                                int max_q_len, int n_q, int n_kv, int d, float scale, int window,
-                                                int page_tokens, int num_pages, int* status, cudaStream_t stream) {
+// `weights`, `chunk`, `bias`: see pingpong::Rules (0, 0, null: the reference's layer); a window and a
+// chunk exclude each other; the sigmoid rule needs one fp32 bias per query head.
+extern "C" int leone_attention_prefill_pingpong_rules(const void* qkv, int row_stride, void* out, int out_stride,
+                                                      const void* k_pool, const void* v_pool, const int* block_table,
+                                                      int table_width, const int* q_start, const int* ctx_len,
+                                                      int n_seqs, int max_q_len, int n_q, int n_kv, int d, float scale,
+                                                      int window, int weights, int chunk, const float* bias,
+                                                      int page_tokens, int num_pages, int* status, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  if (weights < 0 || weights > 2 || chunk < 0 || (chunk > 0 && window > 0) || (weights == 2 && bias == nullptr) || !(scale > 0.f))
+    return kRefusedSize;
+  const pingpong::Rules rules{weights, chunk, bias};
   if (d != 64 && d != 128) return kRefusedSize;
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > pingpong::kRows) return kRefusedSize;
   if (page_tokens <= 0 || table_width <= 0 || n_seqs > 65535) return kRefusedSize;
@@ -597,7 +631,17 @@ extern "C" int leone_attention_prefill_pingpong(const void* qkv, int row_stride,
                          page_tokens, num_pages, n_kv};
   if (d == 64)
     return pingpong::launch<64>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, out_stride, pa, q_start,
-                                ctx_len, n_seqs, n_q, max_q_len, scale, window, status, stream);
+                                ctx_len, n_seqs, n_q, max_q_len, scale, window, rules, status, stream);
   return pingpong::launch<128>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, out_stride, pa, q_start,
-                               ctx_len, n_seqs, n_q, max_q_len, scale, window, status, stream);
+                               ctx_len, n_seqs, n_q, max_q_len, scale, window, rules, status, stream);
+}
+
+extern "C" int leone_attention_prefill_pingpong(const void* qkv, int row_stride, void* out, int out_stride,
+                                                const void* k_pool, const void* v_pool, const int* block_table,
+                                                int table_width, const int* q_start, const int* ctx_len, int n_seqs,
+                                                int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                                                int page_tokens, int num_pages, int* status, cudaStream_t stream) {
+  return leone_attention_prefill_pingpong_rules(qkv, row_stride, out, out_stride, k_pool, v_pool, block_table,
+                                                table_width, q_start, ctx_len, n_seqs, max_q_len, n_q, n_kv, d, scale,
+                                                window, 0, 0, nullptr, page_tokens, num_pages, status, stream);
 }

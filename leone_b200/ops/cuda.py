@@ -452,6 +452,12 @@ class CudaOps:
         to 64 query heads per KV head (16 in a decode step, whose keys are also split over blocks
         until the SMs are busy)."""
         decode = bool(ctx.decode_only)
+        # prompt portions with head sizes 64 and 128: the tcgen05 prompt kernel takes the rule as a parameter
+        if (dk == dv and not decode and getattr(ctx, "q_start", None) is not None
+                and os.environ.get("LEONE_NO_MASKED_TC", "0") != "1"
+                and self.fast.attention_rules(ctx, qkv, out, n_q, n_kv, dk, scale, mask_size if mask == "window" else 0,
+                                              mask_size if mask == "chunk" else 0, self._WEIGHTS[weights], bias, cache)):
+            return True
         if (qkv.dtype != torch.bfloat16 or os.environ.get("LEONE_NO_MASKED_MMA", "0") == "1"
                 or getattr(ctx, "q_start", None) is None
                 or not self.mixers.leone_attention_masked_mma_supported(n_q, n_kv, dk, dv, 1 if decode else 0)

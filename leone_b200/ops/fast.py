@@ -556,6 +556,25 @@ class FastKernels:
         if code != 0:
             raise RuntimeError(f"prompt attention refused or failed with code {code}")
 
+    def attention_rules(self, ctx, qkv, out, n_q, n_kv, d, scale, window, chunk, weights, bias, cache) -> bool:
+        """Prompt portions and mixed steps of an attention layer with another mask (``chunk``) or
+        weight rule (``weights``: 0 softmax, 1 softmax with a silent member of score 0, 2 sigmoid
+        with a ``bias`` per head) on the tcgen05 prompt kernel: head sizes 64 and 128 with values
+        as wide as keys.  False: not this kernel's case."""
+        g = n_q // n_kv
+        if not (self.attention_supported(qkv.dtype, n_q, n_kv, d, qkv.stride(0)) and self.use_tc_attention
+                and d in (64, 128) and g <= 128 and out.stride(0) % 8 == 0 and not ctx.decode_only):
+            return False
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        code = self.lib.leone_attention_prefill_pingpong_rules(
+            _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt), bt.stride(0),
+            _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs, ctx.max_q_len, n_q, n_kv, d, c_float(scale),
+            int(window or 0), int(weights), int(chunk or 0), _ptr(bias), cache.page_tokens, kp.shape[0],
+            _ptr(ctx.status), self._stream())
+        if code != 0:
+            raise RuntimeError(f"prompt attention refused or failed with code {code}")
+        return True
+
     def _attn_scratch(self, floats: int):
         if self._attn_ws is None or self._attn_ws.numel() < floats:
             self._retire(self._attn_ws)

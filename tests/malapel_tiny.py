@@ -64,8 +64,15 @@ TINY = {
         layer("attention", mixer(18, 6, 16, 16, 0.2, rot_dims=8, base=1000.0, mask=70), None),
         layer("attention_3", mixer(2, 1, 144, 48, 0.08, rot_dims=100, mask=70), moe(24, 6, 6, 1.25, (2, 2))),
         layer("attention_2", mixer(5, 5, 32, 32, 0.17, rot_dims=16), dense(64, 2.5))]},
+    # windows, chunks and the sigmoid rule at the head sizes of the tcgen05 prompt kernel (64 and 128, values as
+    # wide as keys), looped, with a window and a chunk that end inside a key tile
+    "E": {"architecture": "Malapel", "vocab": 180, "width": 128, "norm": {"eps": 1e-6},
+          "loop": {"start": 0, "stop": 2, "times": 2}, "layers": [
+        layer("attention_3", mixer(4, 2, 64, 64, 0.12, rot_dims=32, mask=40), dense(192, 3.0)),
+        layer("attention", mixer(2, 1, 128, 128, 0.09, rot_dims=128, base=50000.0, mask=50), moe(48, 8, 2, 2.0, (4, 2))),
+        layer("attention", mixer(6, 2, 64, 64, 0.12, rot_dims=16, mask=130), dense(96, 1.0))]},
 }
-PAGE_TOKENS = {"A": 4, "B": 8, "C": 16, "D": 32}
+PAGE_TOKENS = {"A": 4, "B": 8, "C": 16, "D": 32, "E": 16}
 
 
 def tiny_config(which):

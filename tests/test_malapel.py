@@ -155,7 +155,7 @@ def test_cache_requests_of_the_mixers():
 
 # -- on the GPU ----------------------------------------------------------------------------------
 @pytest.mark.gpu
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_replay_on_the_gpu(which, dtype, mode):
@@ -174,9 +174,9 @@ def test_replay_on_the_gpu(which, dtype, mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("switch", ["LEONE_NO_MASKED_MMA", "LEONE_NO_EXPERT_MMA", "LEONE_NO_TENSOR_CORES",
+@pytest.mark.parametrize("switch", ["LEONE_NO_MASKED_MMA", "LEONE_NO_MASKED_TC", "LEONE_NO_EXPERT_MMA", "LEONE_NO_TENSOR_CORES",
                                     "LEONE_NO_TILED_ATTENTION", "LEONE_NO_FUSED_NORM"])
-@pytest.mark.parametrize("which", ["C", "D"])
+@pytest.mark.parametrize("which", ["C", "D", "E"])
 def test_bfloat16_kernel_switches(which, switch, monkeypatch):
     """Every bfloat16 kernel has an any-size form behind a switch; with the switch thrown the same
     traces still agree with the plain implementation (prompt portions of 100 tokens and decode)."""
@@ -395,7 +395,8 @@ def test_attention_kernels_against_the_plain_rules():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("n_q,n_kv,dk,dv", [(6, 2, 32, 48), (4, 4, 96, 96), (8, 1, 128, 16), (2, 1, 16, 128)])
+@pytest.mark.parametrize("n_q,n_kv,dk,dv", [(6, 2, 32, 48), (4, 4, 96, 96), (8, 1, 128, 16), (2, 1, 16, 128),
+                                            (8, 2, 128, 128), (3, 1, 64, 64)])
 def test_tensor_core_attention_against_the_plain_rules(n_q, n_kv, dk, dv):
     """The bfloat16 tensor-core kernel alone: three sequences of unequal lengths as prompt portions
     that start in the middle of a sequence, and as a decode step with and without split keys, for
