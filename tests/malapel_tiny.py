@@ -47,7 +47,7 @@ TINY = {
     # every group kept, one expert of three
     "B": {"architecture": "Malapel", "vocab": 131, "width": 72, "norm": {"eps": 3e-6},
           "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [
-        layer("attention", mixer(1, 1, 20, 28, 0.3, rot_dims=12, mask=1), moe(40, 3, 1, 2.5, (3, 3))),
+        layer("attention", mixer(1, 1, 20, 28, 0.3, rot_dims=12, mask=1), moe(36, 3, 1, 2.5, (3, 3))),
         layer("attention_3", mixer(5, 5, 12, 10, 0.35, rot_dims=6, base=100.0, mask=500), dense(100, 0.75)),
         layer("attention_3", mixer(2, 1, 36, 36, 0.2, rot_dims=36, mask=1), dense(60, 4.0)),
         layer("attention", mixer(3, 3, 8, 8, 0.4, rot_dims=2, mask=7), None)]},
