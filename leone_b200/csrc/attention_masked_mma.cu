@@ -24,6 +24,7 @@
 namespace leone {
 
 constexpr int kMmRows = 64, kMmKeys = 64, kMmThreads = 128;
+constexpr int kDecKeys = 32;      // keys per tile in the decode form: smaller tiles, more blocks per SM
 
 __device__ __forceinline__ void ldsm4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -68,16 +69,16 @@ struct MaskedArgs {
   int* status;
 };
 
-// Copies keys j0 .. j0 + 63 of (sequence, kv head) into a tile: K rows of dk, V rows of dv elements.
+// Copies keys j0 .. j0 + keys - 1 of (sequence, kv head) into a tile: K rows of dk, V rows of dv elements.
 // Keys outside [lo, hi] become zeros.  `lanes` threads take part, this one is `me`.
 __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int kvh, int j0, int lo, int hi,
                                              uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int me, int lanes,
-                                             int tok_row) {
+                                             int tok_row, int keys) {
   const int kc = a.dk >> 3, vc = a.dv >> 3;         // 16-byte chunks per row
   // a block's threads pair up on a key row, a warp's lanes take whole rows: one look-up of the
   // row's page per thread, then copies that depend on nothing else
   const int tpr = lanes >= 128 ? 2 : 1, sub = me % tpr;
-  for (int r = me / tpr; r < kMmKeys; r += lanes / tpr) {
+  for (int r = me / tpr; r < keys; r += lanes / tpr) {
     const int j = j0 + r;
     bool ok = j >= lo && j <= hi;
     long long slot = 0;
@@ -99,18 +100,61 @@ __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int k
   }
 }
 
-// One warp, 16 rows, one tile of 64 keys: scores, weights, and the sums into o.  Row `g` (and g + 8)
+// The same by one warp for a tile of up to 32 keys, with coalesced copies: lane r first finds the place
+// of key row r (one look-up in the block table) and leaves it in `slot_s` (32 entries of the warp's
+// own); then consecutive lanes copy consecutive 16-byte pieces of a row, so that one instruction
+// covers whole rows instead of a piece of 32 different ones.
+__device__ __forceinline__ void load_kv_tile_warp(const MaskedArgs& a, int seq, int kvh, int j0, int lo, int hi,
+                                                  uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int lane,
+                                                  int tok_row, int keys, long long* slot_s) {
+  {
+    const int j = j0 + lane;
+    long long slot = -1;
+    if (lane < keys && j >= lo && j <= hi) {
+      const int blk = j / a.page_tokens;
+      const int page = blk < a.table_width ? a.block_table[(size_t)seq * a.table_width + blk] : -1;
+      if (page < 0 || page >= a.num_pages)
+        set_status(a.status, kBadPage, tok_row, page, j);
+      else
+        slot = ((long long)page * a.n_kv + kvh) * a.page_tokens + (j - blk * a.page_tokens);
+    }
+    __syncwarp();                  // the last tile's readers of slot_s are done
+    slot_s[lane] = slot;
+    __syncwarp();
+  }
+  auto copy = [&](const __nv_bfloat16* pool, int width, uint32_t dst, int pitch) {
+    const int chunks = width >> 3;                       // 16-byte pieces per row
+    int r = lane / chunks, w = lane - r * chunks;
+    const int dr = 32 / chunks, dw = 32 - dr * chunks;
+    while (r < keys) {
+      const long long slot = slot_s[r];
+      const bool ok = slot >= 0;
+      cp_async16_zfill(dst + (r * pitch + w * 8) * 2, ok ? (const void*)(pool + slot * width + w * 8) : (const void*)pool, ok);
+      r += dr;
+      w += dw;
+      if (w >= chunks) {
+        w -= chunks;
+        r += 1;
+      }
+    }
+  };
+  copy(a.k_pool, a.dk, k_s, pitch_k);
+  copy(a.v_pool, a.dv, v_s, pitch_v);
+}
+
+// One warp, 16 rows, one tile of NT * 8 keys (64 in the prompt form, 32 in the decode form): scores,
+// weights, and the sums into o.  Row `g` (and g + 8)
 // of the warp sees keys [lo_r, hi_r] (absolute positions); the tile starts at key j0.  `full`
 // (uniform in the warp): every row sees every key of the tile, so no key is tested.  `scale2` is
 // the score scale times log2(e), the bias and the running maximum are in the same units.
-template <int DKT, int DVT>
+template <int DKT, int DVT, int NT>
 __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int dkt,
                                           int dvt, int lane, int j0, bool full, const int (&lo_r)[2],
                                           const int (&hi_r)[2], float scale2, int weights, const float (&bias_r)[2],
                                           float (&m_run)[2], float (&l_run)[2], float (&o)[2 * DVT][4]) {
-  float s[8][4];
+  float s[NT][4];
 #pragma unroll
-  for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+  for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
   const int mi = lane >> 3;
 #pragma unroll
   for (int kt = 0; kt < DKT; ++kt) {
@@ -118,7 +162,7 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
       uint32_t a0, a1, a2, a3;
       ldsm4(q_s + ((lane & 15) * pitch_k + kt * 16 + (lane >> 4) * 8) * 2, a0, a1, a2, a3);
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {
+      for (int np = 0; np < NT / 2; ++np) {
         uint32_t b0, b1, b2, b3;
         ldsm4(k_s + ((np * 16 + (lane & 7) + (mi >> 1) * 8) * pitch_k + kt * 16 + (mi & 1) * 8) * 2, b0, b1, b2, b3);
         mma16816(s[2 * np], a0, a1, a2, a3, b0, b1);
@@ -131,7 +175,7 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
   // Keys a row does not see get the score -inf (scale2 > 0 keeps it), which every rule turns into 0.
   if (!full) {
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int h = i >> 1, j = j0 + n * 8 + 2 * tq + (i & 1);
@@ -140,14 +184,14 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
   }
   if (weights == 2) {
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i)      // the reciprocal of 1 + 2^+inf is 0
         s[n][i] = __frcp_rn(1.f + fast_exp2(-fmaf(s[n][i], scale2, bias_r[i >> 1])));
   } else {
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         s[n][i] *= scale2;
@@ -172,7 +216,7 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
       o[n][3] *= alpha[1];
     }
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float p = fast_exp2(s[n][i] - m_use[i >> 1]);      // 2^-inf = 0 for keys the row does not see
@@ -182,7 +226,7 @@ __device__ __forceinline__ void tile_step(uint32_t q_s, uint32_t k_s, uint32_t v
   }
   // O += P V: P as A fragments (16 keys a step), V^T fragments through ldmatrix.trans
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk) {
+  for (int kk = 0; kk < NT / 2; ++kk) {
     const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
     const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
@@ -236,7 +280,7 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
   const int k_lo = mm_first_seen(a.mask, a.mask_size, pos_first);
   const int n_tiles = (pos_last - k_lo) / kMmKeys + 1;
   load_kv_tile(a, seq, kvh, k_lo, k_lo, pos_last, kv_s, kv_s + kMmKeys * pitch_k * 2, pitch_k, pitch_v, tid, kMmThreads,
-               row0 + tok0);
+               row0 + tok0, kMmKeys);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
   // this thread's two rows
@@ -270,7 +314,7 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
     const uint32_t cur = kv_s + (t & 1) * stage_bytes, nxt = kv_s + ((t + 1) & 1) * stage_bytes;
     if (t + 1 < n_tiles)
       load_kv_tile(a, seq, kvh, k_lo + (t + 1) * kMmKeys, k_lo, pos_last, nxt, nxt + kMmKeys * pitch_k * 2, pitch_k,
-                   pitch_v, tid, kMmThreads, row0 + tok0);
+                   pitch_v, tid, kMmThreads, row0 + tok0, kMmKeys);
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
@@ -282,7 +326,7 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
                      j0 + kMmKeys - 1 >= mm_first_seen(a.mask, a.mask_size, start + tok0 + w_first_tok);
     const bool full = w_all_valid && j0 >= w_lo_max && j0 + kMmKeys - 1 <= w_hi_min;
     if (any)
-      tile_step<DKT, DVT>(q_s + warp * 16 * pitch_k * 2, cur, cur + kMmKeys * pitch_k * 2, pitch_k, pitch_v, dkt, dvt, lane,
+      tile_step<DKT, DVT, 8>(q_s + warp * 16 * pitch_k * 2, cur, cur + kMmKeys * pitch_k * 2, pitch_k, pitch_v, dkt, dvt, lane,
                           j0, full, lo_r, hi_r, a.scale * kLog2e, a.weights, bias_r, m_run, l_run, o);
     __syncthreads();
   }
@@ -315,6 +359,7 @@ attention_masked_decode_kernel(const MaskedArgs a) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ long long slot_s[4][32];
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int g = a.n_q / a.n_kv;
   const int row = a.q_start[seq];
@@ -323,8 +368,8 @@ attention_masked_decode_kernel(const MaskedArgs a) {
   const int pitch_k = a.dk + 8, pitch_v = a.dv + 8;
   const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_raw);
   const uint32_t q_s = base;
-  const uint32_t tile_bytes = kMmKeys * (pitch_k + pitch_v) * 2;
-  const uint32_t my_k = q_s + 16 * pitch_k * 2 + warp * tile_bytes, my_v = my_k + kMmKeys * pitch_k * 2;
+  const uint32_t tile_bytes = kDecKeys * (pitch_k + pitch_v) * 2;
+  const uint32_t my_k = q_s + 16 * pitch_k * 2 + warp * tile_bytes, my_v = my_k + kDecKeys * pitch_k * 2;
   const int dkt = a.dk >> 4, dvt = a.dv >> 4;
   {
     const int kc = a.dk >> 3;
@@ -339,7 +384,7 @@ attention_masked_decode_kernel(const MaskedArgs a) {
     __syncthreads();
   }
   const int k_lo = mm_first_seen(a.mask, a.mask_size, pos);
-  const int n_tiles = (pos - k_lo) / kMmKeys + 1;
+  const int n_tiles = (pos - k_lo) / kDecKeys + 1;
   const int per_split = (n_tiles + a.splits - 1) / a.splits;
   const int t_begin = split * per_split, t_end = min(n_tiles, t_begin + per_split);
   const int gq = lane >> 2;
@@ -357,12 +402,12 @@ attention_masked_decode_kernel(const MaskedArgs a) {
 #pragma unroll
   for (int n = 0; n < 2 * DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   for (int t = t_begin + warp; t < t_end; t += 4) {
-    const int j0 = k_lo + t * kMmKeys;
-    load_kv_tile(a, seq, kvh, j0, k_lo, pos, my_k, my_v, pitch_k, pitch_v, lane, 32, row);
+    const int j0 = k_lo + t * kDecKeys;
+    load_kv_tile_warp(a, seq, kvh, j0, k_lo, pos, my_k, my_v, pitch_k, pitch_v, lane, row, kDecKeys, slot_s[warp]);
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
-    tile_step<DKT, DVT>(q_s, my_k, my_v, pitch_k, pitch_v, dkt, dvt, lane, j0, false, lo_r, hi_r, a.scale * kLog2e,
+    tile_step<DKT, DVT, kDecKeys / 8>(q_s, my_k, my_v, pitch_k, pitch_v, dkt, dvt, lane, j0, false, lo_r, hi_r, a.scale * kLog2e,
                         a.weights, bias_r, m_run, l_run, o);
     __syncwarp();
   }
@@ -462,7 +507,7 @@ static int launch_masked(const MaskedArgs& a, int n_seqs, int max_q_len, bool de
   const int pitch_k = a.dk + 8, pitch_v = a.dv + 8;
   const int g = a.n_q / a.n_kv;
   if (decode) {
-    size_t smem = (size_t)16 * pitch_k * 2 + 4 * (size_t)kMmKeys * (pitch_k + pitch_v) * 2;
+    size_t smem = (size_t)16 * pitch_k * 2 + 4 * (size_t)kDecKeys * (pitch_k + pitch_v) * 2;
     const size_t merge = (size_t)4 * 16 * (a.dv + 2) * sizeof(float);
     if (merge > smem) smem = merge;
     static size_t configured = 0;

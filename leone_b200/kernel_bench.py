@@ -4,6 +4,9 @@
     python -m leone_b200.kernel_bench decode-attention --batch 8 --context 2048
     python -m leone_b200.kernel_bench prefill-attention --tokens 2048
     python -m leone_b200.kernel_bench layer-shapes --m 8          # every product of a Qwen3-8B layer
+    python -m leone_b200.kernel_bench masked-attention --tokens 2048 --mask window --mask-size 1024 --weights sigmoid
+    python -m leone_b200.kernel_bench masked-attention --decode --batch 8 --context 2048 --mask chunk \
+        --mask-size 1024 --weights softmax_plus_one
 
 The reference's ``--profile-decode`` prints per-operation microseconds and GEMV GB/s by shape
 (crates/leone-cli/src/main.rs:2918-2995); this is the same kind of table for this engine's
@@ -211,6 +214,42 @@ def bench_prefill_attention(ops, tokens, n_q, n_kv, d, page_tokens, reps, warmup
     return dict(kernel="attention_prefill", tokens=tokens, us=ms * 1e3, tflops=flops / ms / 1e9)
 
 
+def bench_masked_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, mask, size, weights, page_tokens, reps, warmup):
+    """Attention with a mask and a weight rule (``CudaOps.attention_masked``): one prompt of
+    ``tokens`` tokens, or with ``batch`` a decode step of that many sequences at ``context`` keys."""
+    decode = batch > 0
+    seqs, length = (batch, context) if decode else (1, tokens)
+    blocks = -(-length // page_tokens)
+    k_pool = torch.randn((seqs * blocks, n_kv, page_tokens, dk), device=DEV).to(torch.bfloat16)
+    v_pool = torch.randn((seqs * blocks, n_kv, page_tokens, dv), device=DEV).to(torch.bfloat16)
+    table = torch.randperm(seqs * blocks, device=DEV).to(torch.int32).view(seqs, blocks)
+    n = seqs if decode else tokens
+    qkv = torch.randn((n, (n_q + n_kv) * dk + n_kv * dv), device=DEV).to(torch.bfloat16)
+    out = torch.empty((n, n_q * dv), device=DEV, dtype=torch.bfloat16)
+    ctx = types.SimpleNamespace(
+        q_start=torch.arange(seqs + 1, device=DEV, dtype=torch.int32) * (1 if decode else tokens),
+        ctx_len=torch.full((seqs,), length, device=DEV, dtype=torch.int32),
+        status=torch.zeros(4, device=DEV, dtype=torch.int32), n_seqs=seqs, max_q_len=1 if decode else tokens,
+        max_ctx_len=length, decode_only=decode)
+    ctx.positions = (ctx.ctx_len - 1) if decode else torch.arange(tokens, device=DEV, dtype=torch.int32)
+    ctx.seq_of_token = torch.arange(seqs, device=DEV, dtype=torch.int32) if decode else \
+        torch.zeros(tokens, device=DEV, dtype=torch.int32)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=page_tokens)
+    bias = torch.zeros(n_q, device=DEV) if weights == "sigmoid" else None
+    ms = _time(lambda: ops.attention_masked(ctx, qkv, out, n_q, n_kv, dk, dv, dk ** -0.5, mask, size, weights, bias, cache),
+               reps, warmup)
+    # keys a query at position p sees
+    def seen(p):
+        return p + 1 if mask == "causal" else (min(p + 1, size) if mask == "window" else p % size + 1)
+    keys = seqs * seen(length - 1) if decode else sum(seen(p) for p in range(tokens))
+    row = dict(kernel="attention_masked", mask=mask, size=size, weights=weights, dk=dk, dv=dv, us=ms * 1e3)
+    if decode:
+        row.update(batch=batch, context=context, gbs=keys * n_kv * (dk + dv) * 2.0 / ms / 1e6)
+    else:
+        row.update(tokens=tokens, tflops=2.0 * n_q * (dk + dv) * keys / ms / 1e9)
+    return row
+
+
 def bench_sampling(ops, rows, vocab, stages, reps, warmup):
     """The sampler's truncation pipeline (sort, stages, draw) on ``rows`` rows of ``vocab`` logits;
     wall time with a synchronize on both sides (the call makes dozens of small launches)."""
@@ -232,7 +271,13 @@ def bench_sampling(ops, rows, vocab, stages, reps, warmup):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m leone_b200.kernel_bench")
-    ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes", "sampling"])
+    ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes", "sampling",
+                                     "masked-attention"])
+    ap.add_argument("--mask", choices=["causal", "window", "chunk"], default="window")
+    ap.add_argument("--mask-size", type=int, default=1024)
+    ap.add_argument("--weights", choices=["softmax", "softmax_plus_one", "sigmoid"], default="sigmoid")
+    ap.add_argument("--value-dim", type=int, default=0, help="masked-attention: value width (default: the head size)")
+    ap.add_argument("--decode", action="store_true", help="masked-attention: a decode step of --batch sequences")
     ap.add_argument("--stages", default="top_k=40,top_p=0.95",
                     help="sampling: truncation stages in order, e.g. top_k=40,typical=0.9")
     ap.add_argument("--vocab", type=int, default=151936)
@@ -311,6 +356,10 @@ def main(argv=None) -> int:
     elif args.what == "sampling":
         stages = [(n, float(v)) for n, v in (item.split("=") for item in args.stages.split(",") if item)]
         rows.append(bench_sampling(ops, args.batch, args.vocab, stages, args.reps, args.warmup))
+    elif args.what == "masked-attention":
+        rows.append(bench_masked_attention(ops, args.tokens, args.batch if args.decode else 0, args.context, args.heads,
+                                           args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.mask,
+                                           args.mask_size, args.weights, args.page_tokens, args.reps, args.warmup))
     elif args.what == "decode-attention":
         rows.append(bench_decode_attention(ops, args.batch, args.context, args.heads, args.kv_heads,
                                            args.head_dim, args.page_tokens, args.reps, args.warmup, flush, args.prep))

@@ -467,8 +467,8 @@ class CudaOps:
         splits, partial = 1, None
         if decode:
             keys = min(int(mask_size), ctx.max_ctx_len) if mask != "causal" else ctx.max_ctx_len
-            tiles = -(-keys // 64) + 1
-            splits = max(1, min(64, tiles // 4, (2 * 148) // max(ctx.n_seqs * n_kv, 1)))
+            tiles = -(-keys // 32) + 1                # the decode form's tiles hold 32 keys, a block has four warps
+            splits = max(1, min(64, tiles // 8, (3 * 148) // max(ctx.n_seqs * n_kv, 1)))
             if splits > 1:
                 self.mixers.leone_attention_masked_mma_scratch.restype = ctypes.c_longlong
                 need = int(self.mixers.leone_attention_masked_mma_scratch(ctx.n_seqs, n_kv, dv, splits))
