@@ -530,18 +530,20 @@ def test_clamped_gate_against_the_plain_formula():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("which", ["A", "C", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_greedy_generation_through_the_scheduler(dtype, tmp_path):
-    """generate(): admission, prompt portions mixed with decode, captured decode steps, finish."""
+def test_greedy_generation_through_the_scheduler(dtype, which, tmp_path):
+    """generate(): admission, prompt portions mixed with decode, captured decode steps (with the
+    looped layers, their injections and windows whose pages go back while decoding), finish."""
     from leone_b200 import generate
     from leone_b200.weights.safetensors import write_safetensors
     folder = str(tmp_path / "model")
-    cfg = tiny_config("C")
+    cfg = tiny_config(which)
     cfg.write(folder)
-    tensors = tiny_tensors("C")
+    tensors = tiny_tensors(which)
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
-    model = _plain("C", tensors, dtype == "bfloat16")
-    prompts = [replay.random_tokens(256, n, 60 + n) for n in (1, 9, 40, 23, 5)]
+    model = _plain(which, tensors, dtype == "bfloat16")
+    prompts = [replay.random_tokens(TINY[which]["vocab"], n, 60 + n) for n in (1, 9, 40, 23, 5)]
     for kw in (dict(), dict(prefill_chunk=7, max_batch_tokens=16, use_graphs=False, prefill_first=False)):
         got = generate(folder, prompts, 10, dtype=dtype, eos_token_id=-1, max_running=3, **kw)
         for p, toks in zip(prompts, got):
