@@ -185,12 +185,18 @@ template <int D> constexpr int smem_bytes() {
   return 2 * kRows * D * 2 + 4 * kKeys * D * 2 + 2 * 2 * kKeys * 8 + 16 * 8 + 1024;
 }
 
-template <int D>
+// kRules = false: the reference's layer; the rules are then compile-time constants and the kernel is
+// the one it was before they became parameters.
+template <int D, bool kRules>
 __global__ void __launch_bounds__(kBlockThreads)
 attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                                   __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
                                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, int n_q,
-                                  float scale, int window, Rules rules, int* status) {
+                                  float scale, int window, Rules rules_in, int* status) {
+  struct {
+    int weights, chunk;
+    const float* bias;
+  } const rules{kRules ? rules_in.weights : 0, kRules ? rules_in.chunk : 0, kRules ? rules_in.bias : nullptr};
   constexpr int kTileBytes = kKeys * D * 2;             // one K or V tile; a Q tile has the same size
   constexpr int kTmemCols = 512;
   constexpr int kChunks = D / 8;                        // 16-byte chunks per row
@@ -584,13 +590,13 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
   }
 }
 
-template <int D>
-int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride, const PagedArgs& pa,
-           const int* q_start, const int* ctx_len, int n_seqs, int n_q, int max_q_len, float scale, int window,
-           const Rules& rules, int* status, cudaStream_t stream) {
+template <int D, bool kRules>
+int launch_form(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride, const PagedArgs& pa,
+                const int* q_start, const int* ctx_len, int n_seqs, int n_q, int max_q_len, float scale, int window,
+                const Rules& rules, int* status, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_pingpong_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_pingpong_kernel<D, kRules>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -598,8 +604,19 @@ int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out
   const int g = n_q / pa.n_kv;
   const int tq = kRows / g;
   dim3 grid(((max_q_len + 2 * tq - 1) / (2 * tq)) * pa.n_kv, 1, n_seqs);
-  return launch_kernel(attention_prefill_pingpong_kernel<D>, grid, dim3(kBlockThreads), smem_bytes<D>(), stream,
+  return launch_kernel(attention_prefill_pingpong_kernel<D, kRules>, grid, dim3(kBlockThreads), smem_bytes<D>(), stream,
                        qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, rules, status);
+}
+
+template <int D>
+int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride, const PagedArgs& pa,
+           const int* q_start, const int* ctx_len, int n_seqs, int n_q, int max_q_len, float scale, int window,
+           const Rules& rules, int* status, cudaStream_t stream) {
+  if (rules.weights != 0 || rules.chunk != 0)
+    return launch_form<D, true>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale,
+                                window, rules, status, stream);
+  return launch_form<D, false>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale,
+                               window, rules, status, stream);
 }
 
 }  // namespace pingpong
